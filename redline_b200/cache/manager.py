@@ -98,6 +98,10 @@ class GroupInfo:
     def window(self) -> int:
         return self.spec.window if self.spec.kind == "window" else 0
 
+    @property
+    def keep_first(self) -> int:
+        return self.spec.keep_first if self.spec.kind == "window" else 0
+
 
 class RequestCache:
     """What one request holds: a state slot and, per group, a block table (page id per block index; 0
@@ -149,6 +153,9 @@ class CacheManager:
                                          _i32_array([g.window for g in self.groups]), page_size, num_state_slots)
         if not self._h:
             raise CacheError("the cache manager could not be created")
+        for gi, g in enumerate(self.groups):
+            if g.keep_first > 0 and self._lib.rl_hc_set_keep_first(self._h, gi, g.keep_first) != 0:
+                raise CacheError(f"group {gi}: the kept first tokens could not be set")
         self._open: Dict[object, RequestCache] = {}
         self.on_open = None   # called with the RequestCache of every newly opened request
 
@@ -231,7 +238,7 @@ class CacheManager:
     def release_passed(self, rc: RequestCache, num_computed: int) -> int:
         """After ``num_computed`` positions are in the cache: in window groups, frees the
         pages whose keys no later token can see (key j is dead when j <= n - window for
-        the next position n).  Returns how many pages were freed."""
+        the next position n; the pages of the group's kept first tokens stay).  Returns how many pages were freed."""
         n = self._lib.rl_hc_release_passed(self._h, rc.rid, num_computed)
         if n < 0:
             raise CacheError(f"request {rc.key!r}: releasing pages failed ({n})")

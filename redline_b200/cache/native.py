@@ -64,6 +64,7 @@ def lib() -> ctypes.CDLL:
             "rl_pool_is_held": (c_int, [c_void_p, c_int]),
             "rl_hc_create": (c_void_p, [c_int, i32p, i32p, c_int, c_int]),
             "rl_hc_destroy": (None, [c_void_p]),
+            "rl_hc_set_keep_first": (c_int, [c_void_p, c_int, c_int]),
             "rl_hc_open": (c_int, [c_void_p]),
             "rl_hc_close": (c_int, [c_void_p, c_int, POINTER(c_int)]),
             "rl_hc_reserve": (c_int, [c_void_p, c_int, c_int]),

@@ -213,3 +213,163 @@ class LlamaConfig(ModelConfig):
             "eos_token_id": eos,
             "torch_dtype": "bfloat16",
         }
+
+
+# --------------------------------------------------------------------------- Kapitar
+
+@dataclass(frozen=True)
+class KapitarMask:
+    size: int                 # a key is visible while the query is less than so many positions ahead of it
+    keep_first: int = 0       # ... and the first so many keys of the sequence always are
+
+
+@dataclass(frozen=True)
+class KapitarAttention:
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    softcap: float
+    diff: float
+    mask: KapitarMask
+
+
+@dataclass(frozen=True)
+class KapitarLightning:
+    heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]
+
+
+@dataclass(frozen=True)
+class KapitarMLP:
+    kind: str                 # dense | moe
+    ff: int                   # dense: width of the layer; moe: of one expert
+    experts: int = 0
+    top: int = 0
+    groups: int = 1
+    groups_keep: int = 1
+    shared_ff: int = 0        # 0: no shared expert
+
+
+@dataclass(frozen=True)
+class KapitarLayer:
+    type: str                 # attention | lightning
+    mixer: Any
+    mlp: Optional[KapitarMLP]
+
+
+@dataclass(frozen=True)
+class KapitarConfig(ModelConfig):
+    """``Kapitar``: a decoder whose layers norm (layer norm, weight only) the input and the output of every
+    sublayer; mixers are differential attention (two capped score maps over shared values, a window that
+    keeps the first tokens, no rotation) or linear attention with a per-head decay; feed-forwards are dense
+    (squared ReLU) or routed (sigmoid router, groups of experts, a shared expert, erf GELU); the head is the
+    embedding table.  Its config.json lists the layers one by one under ``layers``."""
+
+    norm_eps: float = 1e-6
+    layers: Tuple[KapitarLayer, ...] = ()
+    raw: Optional[Dict[str, Any]] = field(default=None, compare=False, repr=False)
+
+    @classmethod
+    def from_hf(cls, cfg: Dict[str, Any], model_dir: Optional[str] = None) -> "KapitarConfig":
+        layers: List[KapitarLayer] = []
+        for i, entry in enumerate(_need(cfg, "layers")):
+            where = f"layers[{i}]"
+            kind = _need(entry, "type", where)
+            m = _need(entry, "mixer", where)
+            if kind == "attention":
+                mask = _need(m, "mask", where + ".mixer")
+                mixer: Any = KapitarAttention(
+                    heads=int(_need(m, "heads", where)), kv_heads=int(m.get("kv_heads") or m["heads"]),
+                    dim=int(_need(m, "dim", where)), vdim=int(_need(m, "vdim", where)),
+                    scale=float(_need(m, "scale", where)), softcap=float(_need(m, "softcap", where)),
+                    diff=float(_need(m, "diff", where)),
+                    mask=KapitarMask(int(_need(mask, "size", where + ".mixer.mask")), int(mask.get("keep_first", 0))))
+            elif kind == "lightning":
+                mixer = KapitarLightning(heads=int(_need(m, "heads", where)), dim=int(_need(m, "dim", where)),
+                                         vdim=int(_need(m, "vdim", where)),
+                                         decay=tuple(float(d) for d in _need(m, "decay", where)))
+            else:
+                raise ConfigError(f"{where}: mixer type '{kind}' is not supported (attention, lightning)")
+            mlp = entry.get("mlp")
+            ff: Optional[KapitarMLP] = None
+            if mlp is not None:
+                mk = _need(mlp, "kind", where + ".mlp")
+                if mk == "dense":
+                    ff = KapitarMLP("dense", int(_need(mlp, "ff", where + ".mlp")))
+                elif mk == "moe":
+                    r = _need(mlp, "router", where + ".mlp")
+                    groups = r.get("groups") or {}
+                    shared = mlp.get("shared") or {}
+                    ff = KapitarMLP("moe", int(_need(_need(mlp, "expert", where + ".mlp"), "ff", where + ".mlp.expert")),
+                                    experts=int(_need(r, "experts", where + ".mlp.router")),
+                                    top=int(_need(r, "top", where + ".mlp.router")),
+                                    groups=int(groups.get("count", 1)), groups_keep=int(groups.get("keep", groups.get("count", 1))),
+                                    shared_ff=int(shared.get("ff", 0)))
+                else:
+                    raise ConfigError(f"{where}.mlp: kind '{mk}' is not supported (dense, moe)")
+            layers.append(KapitarLayer(kind, mixer, ff))
+        eos = cfg.get("eos_token_id")
+        eos = [] if eos is None else ([eos] if isinstance(eos, int) else list(eos))
+        bos = cfg.get("bos_token_id")
+        c = cls(architecture="Kapitar", vocab_size=int(_need(cfg, "vocab")), hidden_size=int(_need(cfg, "width")),
+                max_position_embeddings=int(cfg.get("max_positions", 1 << 30)),
+                bos_token_id=int(bos) if bos is not None else -1, eos_token_ids=tuple(int(e) for e in eos),
+                norm_eps=float(_need(_need(cfg, "norm"), "eps", "norm")), layers=tuple(layers), raw=dict(cfg))
+        c.validate()
+        return c
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
+            raise ConfigError("vocab, width and the number of layers must be positive")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            if m.heads <= 0 or m.dim <= 0 or m.vdim <= 0:
+                raise ConfigError(f"layers[{i}]: heads, dim and vdim must be positive")
+            if layer.type == "attention":
+                if m.kv_heads <= 0 or m.heads % m.kv_heads != 0:
+                    raise ConfigError(f"layers[{i}]: heads ({m.heads}) must be a multiple of kv_heads ({m.kv_heads})")
+                if m.mask.size <= 0 or m.mask.keep_first < 0 or not m.softcap > 0:
+                    raise ConfigError(f"layers[{i}]: mask.size and softcap must be positive, keep_first not negative")
+            elif len(m.decay) != m.heads:
+                raise ConfigError(f"layers[{i}]: {m.heads} heads need as many decays, got {len(m.decay)}")
+            f = layer.mlp
+            if f is not None and f.kind == "moe":
+                if f.experts <= 0 or f.groups <= 0 or f.experts % f.groups != 0 or not 1 <= f.groups_keep <= f.groups:
+                    raise ConfigError(f"layers[{i}].mlp: {f.experts} experts do not form {f.groups} equal groups "
+                                      f"of which {f.groups_keep} stay")
+                if not 1 <= f.top <= f.groups_keep * (f.experts // f.groups):
+                    raise ConfigError(f"layers[{i}].mlp: top {f.top} experts cannot be chosen")
+
+    def to_hf(self) -> Dict[str, Any]:
+        layers = []
+        for layer in self.layers:
+            m = layer.mixer
+            if layer.type == "attention":
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
+                         "softcap": m.softcap, "diff": m.diff, "mask": {"size": m.mask.size, "keep_first": m.mask.keep_first}}
+            else:
+                mixer = {"heads": m.heads, "dim": m.dim, "vdim": m.vdim, "decay": list(m.decay)}
+            f = layer.mlp
+            if f is None:
+                mlp = None
+            elif f.kind == "dense":
+                mlp = {"kind": "dense", "ff": f.ff}
+            else:
+                mlp = {"kind": "moe", "expert": {"ff": f.ff},
+                       "router": {"experts": f.experts, "top": f.top, "groups": {"count": f.groups, "keep": f.groups_keep}}}
+                if f.shared_ff > 0:
+                    mlp["shared"] = {"ff": f.shared_ff}
+            layers.append({"type": layer.type, "mixer": mixer, "mlp": mlp})
+        out = {"architecture": "Kapitar", "vocab": self.vocab_size, "width": self.hidden_size,
+               "norm": {"eps": self.norm_eps}, "layers": layers}
+        if self.bos_token_id >= 0:
+            out["bos_token_id"] = self.bos_token_id
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out

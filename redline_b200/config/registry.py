@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``architectures[0]`` of config.json)
+"""One registry from an architecture's name (``architectures[0]`` or ``architecture`` of config.json)
 to its configuration class and its factory of a ``ModelSpec``.
 
 Adding an architecture = one call of ``register_architecture`` with a function that
@@ -48,8 +48,10 @@ def _ensure_builtin() -> None:
 
 def config_from_dict(cfg: Dict[str, Any], model_dir: Optional[str] = None) -> ModelConfig:
     archs = cfg.get("architectures")
+    if not archs and isinstance(cfg.get("architecture"), str):      # some designs name theirs in the singular
+        archs = [cfg["architecture"]]
     if not archs:
-        raise ConfigError("config.json has no 'architectures'")
+        raise ConfigError("config.json has neither 'architectures' nor 'architecture'")
     return get_architecture(archs[0]).config_from_hf(cfg, model_dir)
 
 

@@ -1,0 +1,565 @@
+// Causal attention over the paged cache in its general form: key size D and value size DV of their
+// own, M score maps per head over the same values (M = 2: differential attention), an optional
+// tanh cap on the scores, a sliding window that keeps the first tokens of the sequence visible, and
+// an optional unit-RMS norm of every head's output.  No positions enter the scores here (a rotary
+// encoding would be applied to q and k before the cache write).
+//
+//   query row (h, m) of token i:   s_j = cap * tanh(scale * q_{h,m} . k_{g,m,j} / cap),  g = h / (H / G)
+//   key j is visible from i when    j <= i and (i - j < window or j < keep_first)      (window 0: all)
+//   a_{h,m} = softmax_j(s) V_g
+//   M = 1:  o_h = a_{h,0};          M = 2:  o_h = a_{h,0} - lambda * a_{h,1}
+//   unit_norm:  o_h <- o_h / sqrt(mean(o_h^2) + eps) * post_scale
+//
+// Layouts: q [tokens, q_stride] with row (h, m) at column (h * M + m) * D; the key cache
+// [pages, G * M, page_size, D] (kv head g's map m is head g * M + m); the value cache
+// [pages, G, page_size, DV]; out [tokens, out_stride] with head h at column h * DV.
+//
+// Scores, softmax, the combination of the maps and the norm are float32 for both element types.
+// Single tokens: one CTA per (128-key partition, kv head, item) over absolute partitions, so a row's
+// sums do not depend on what else is in the launch; a second kernel merges the partitions of a head's
+// maps, combines them and norms.  Prompt portions: one CTA per (32 query rows, head), both maps in
+// turn over the visible key tiles, combination and norm in the epilogue.
+#include "common.cuh"
+
+#if !defined(RL_QK_DIM) || !defined(RL_V_DIM) || !defined(RL_MAPS)
+#error "compile with -DRL_QK_DIM=<key size> -DRL_V_DIM=<value size> -DRL_MAPS=<1 or 2>"
+#endif
+
+namespace rl {
+
+constexpr int kD = RL_QK_DIM, kDV = RL_V_DIM, kM = RL_MAPS;
+static_assert(kM == 1 || kM == 2, "one or two score maps");
+static_assert(kD >= 1 && kD <= 256 && kDV >= 4 && kDV <= 256 && kDV % 4 == 0, "sizes out of range");
+constexpr int kPart = 128;
+constexpr int kThreads = 128;
+constexpr int kLPK = 8;                      // lanes that share a key
+constexpr int kKeysPerIter = kThreads / kLPK;
+constexpr int kRows = 4;                     // query rows per pass over the keys
+
+struct MaskArgs {
+  int window, keep_first;
+};
+
+__device__ __forceinline__ bool key_visible(int j, int i, const MaskArgs& mk) {
+  return j <= i && (mk.window <= 0 || i - j < mk.window || j < mk.keep_first);
+}
+// Whether keys [lo, hi) hold one that position i sees.
+__device__ __forceinline__ bool range_visible(int lo, int hi, int i, const MaskArgs& mk) {
+  if (lo > i || lo >= hi) return false;
+  if (mk.window <= 0) return true;
+  return lo < mk.keep_first || hi > i - mk.window + 1;
+}
+
+template <typename T>
+__device__ __forceinline__ void load_row(const T* __restrict__ p, int n, float* out) {
+  // n elements from p (16-byte aligned when n is a multiple of the vector width)
+  constexpr int VEC = Vec16<T>::N;
+  if (n % VEC == 0) {
+    for (int c = 0; c < n; c += VEC) load16(p + c, out + c);
+  } else {
+    for (int c = 0; c < n; ++c) out[c] = to_float(p[c]);
+  }
+}
+
+template <typename T>
+struct MapsDecodeArgs {
+  const T* q;
+  int q_stride;
+  const T* kcache;
+  const T* vcache;
+  const int32_t* block_table;
+  int max_blocks;
+  const int4* items;     // (token index, sequence index, context length, 0)
+  float* part_o;         // [items, H * M, max_parts, DV]
+  float* part_ml;        // [items, H * M, max_parts, 2]
+  int max_parts;
+  T* out;
+  int out_stride;
+  int heads, kv_heads, page_size;
+  MaskArgs mask;
+  float scale, softcap, lambda, post_scale, eps;
+  int unit_norm;
+};
+
+// Lane l of the 8 that share a key takes elements l, l + 8, ... of the key in pieces of E elements.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maps_decode_kernel(const MapsDecodeArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int E = (kD % VEC == 0) ? VEC : 1;          // piece of a key
+  constexpr int CH = kD / E;
+  constexpr int CPL = (CH + kLPK - 1) / kLPK;
+  constexpr int EVV = (kDV % VEC == 0) ? VEC : 1;         // piece of a value row
+  constexpr int CHV = kDV / EVV;
+  constexpr int CPLV = (CHV + kLPK - 1) / kLPK;
+  __shared__ float qs[kRows][kD];
+  __shared__ float sc[kRows][kPart];
+  __shared__ float red[kThreads / 32][kRows][kDV];
+  __shared__ float stat_m[kRows], stat_l[kRows];
+
+  const int part = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
+  const int4 info = a.items[item];
+  const int tok = info.x, seq = info.y, ctx = info.z;
+  const int me = ctx - 1;                                // the query's position
+  const int base = part * kPart;
+  const int j_hi = min(ctx, base + kPart);
+  if (!range_visible(base, j_hi, me, a.mask)) return;
+  const int G = a.heads / a.kv_heads;
+  const int lane8 = threadIdx.x % kLPK, slot = threadIdx.x / kLPK;
+  const int warp = threadIdx.x >> 5;
+  const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
+  const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+
+  for (int m = 0; m < kM; ++m) {
+    const int khead = kvh * kM + m;
+    for (int g0 = 0; g0 < G; g0 += kRows) {
+      const int ng = min(kRows, G - g0);
+      __syncthreads();
+      for (int i = threadIdx.x; i < kRows * kD; i += kThreads) {
+        const int g = i / kD, d = i - g * kD;
+        qs[g][d] = g < ng ? to_float(a.q[static_cast<size_t>(tok) * a.q_stride +
+                                         ((kvh * G + g0 + g) * kM + m) * kD + d]) * a.scale
+                          : 0.f;
+      }
+      __syncthreads();
+      // ---- scores (every lane of a warp makes the same number of trips: the shuffles need all of them)
+      for (int jb = base; jb < j_hi; jb += kKeysPerIter) {
+        const int j = jb + slot;
+        const bool live = j < j_hi && key_visible(j, me, a.mask);
+        const size_t page = live ? bt[j / a.page_size] : 0;
+        const T* kp = a.kcache + ((page * (a.kv_heads * kM) + khead) * a.page_size + j % a.page_size) * kD;
+        float dot[kRows];
+#pragma unroll
+        for (int g = 0; g < kRows; ++g) dot[g] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+          const int ch = lane8 + c * kLPK;
+          if (live && ch < CH) {
+            float kf[E];
+            if (E == 1) kf[0] = to_float(kp[ch]);
+            else load16(kp + ch * E, kf);
+#pragma unroll
+            for (int g = 0; g < kRows; ++g) {
+#pragma unroll
+              for (int e = 0; e < E; ++e) dot[g] += kf[e] * qs[g][ch * E + e];
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < kRows; ++g) {
+          float v = dot[g];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          if (lane8 == 0 && j < j_hi) {
+            if (a.softcap > 0.f) v = a.softcap * tanhf(v * inv_cap);
+            sc[g][j - base] = live ? v : -INFINITY;
+          }
+        }
+      }
+      __syncthreads();
+      // ---- softmax statistics of this partition, one warp per row
+      for (int g = warp; g < ng; g += kThreads / 32) {
+        float mx = -INFINITY;
+        for (int j = base + (threadIdx.x & 31); j < j_hi; j += 32) mx = fmaxf(mx, sc[g][j - base]);
+        mx = warp_max(mx);
+        float l = 0.f;
+        for (int j = base + (threadIdx.x & 31); j < j_hi; j += 32) {
+          const float p = expf(sc[g][j - base] - mx);      // masked keys: exp(-inf) = 0
+          sc[g][j - base] = p;
+          l += p;
+        }
+        l = warp_sum(l);
+        if ((threadIdx.x & 31) == 0) {
+          stat_m[g] = mx;
+          stat_l[g] = l;
+        }
+      }
+      __syncthreads();
+      // ---- P V
+      float acc[kRows][CPLV][EVV];
+#pragma unroll
+      for (int g = 0; g < kRows; ++g)
+#pragma unroll
+        for (int c = 0; c < CPLV; ++c)
+#pragma unroll
+          for (int e = 0; e < EVV; ++e) acc[g][c][e] = 0.f;
+      for (int j = base + slot; j < j_hi; j += kKeysPerIter) {
+        if (!key_visible(j, me, a.mask)) continue;
+        const size_t page = bt[j / a.page_size];
+        const T* vp = a.vcache + ((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV;
+        float p[kRows];
+#pragma unroll
+        for (int g = 0; g < kRows; ++g) p[g] = g < ng ? sc[g][j - base] : 0.f;
+#pragma unroll
+        for (int c = 0; c < CPLV; ++c) {
+          const int ch = lane8 + c * kLPK;
+          if (ch < CHV) {
+            float vf[EVV];
+            if (EVV == 1) vf[0] = to_float(vp[ch]);
+            else load16(vp + ch * EVV, vf);
+#pragma unroll
+            for (int g = 0; g < kRows; ++g)
+#pragma unroll
+              for (int e = 0; e < EVV; ++e) acc[g][c][e] += p[g] * vf[e];
+          }
+        }
+      }
+      // lanes 8 and 16 apart hold other keys of the same piece
+#pragma unroll
+      for (int g = 0; g < kRows; ++g)
+#pragma unroll
+        for (int c = 0; c < CPLV; ++c)
+#pragma unroll
+          for (int e = 0; e < EVV; ++e) {
+            float v = acc[g][c][e];
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            acc[g][c][e] = v;
+          }
+      if ((threadIdx.x & 31) < kLPK) {
+#pragma unroll
+        for (int g = 0; g < kRows; ++g)
+#pragma unroll
+          for (int c = 0; c < CPLV; ++c) {
+            const int ch = lane8 + c * kLPK;
+            if (ch < CHV) {
+#pragma unroll
+              for (int e = 0; e < EVV; ++e) red[warp][g][ch * EVV + e] = acc[g][c][e];
+            }
+          }
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < ng * kDV; i += kThreads) {
+        const int g = i / kDV, d = i - g * kDV;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) v += red[w][g][d];
+        const int qrow = (kvh * G + g0 + g) * kM + m;
+        const size_t row = (static_cast<size_t>(item) * (a.heads * kM) + qrow) * a.max_parts + part;
+        a.part_o[row * kDV + d] = v;
+        if (d == 0) {
+          a.part_ml[row * 2] = stat_m[g];
+          a.part_ml[row * 2 + 1] = stat_l[g];
+        }
+      }
+    }
+  }
+}
+
+// One CTA per (item, head): merges the visible partitions of each of the head's maps, combines the
+// maps, norms, writes.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maps_merge_kernel(const MapsDecodeArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float o[kDV];
+  __shared__ float scratch[32];
+  const int item = blockIdx.x, head = blockIdx.y;
+  const int4 info = a.items[item];
+  const int tok = info.x, ctx = info.z;
+  const int me = ctx - 1;
+  const int p_hi = me / kPart;
+  for (int d = threadIdx.x; d < kDV; d += kThreads) o[d] = 0.f;
+  __syncthreads();
+  for (int m = 0; m < kM; ++m) {
+    const size_t row0 = (static_cast<size_t>(item) * (a.heads * kM) + head * kM + m) * a.max_parts;
+    float mx = -INFINITY;
+    for (int p = 0; p <= p_hi; ++p)
+      if (range_visible(p * kPart, min(ctx, (p + 1) * kPart), me, a.mask)) mx = fmaxf(mx, a.part_ml[(row0 + p) * 2]);
+    const float coef = m == 0 ? 1.f : -a.lambda;
+    for (int d = threadIdx.x; d < kDV; d += kThreads) {
+      float num = 0.f, den = 0.f;
+      for (int p = 0; p <= p_hi; ++p) {
+        if (!range_visible(p * kPart, min(ctx, (p + 1) * kPart), me, a.mask)) continue;
+        const float w = expf(a.part_ml[(row0 + p) * 2] - mx);
+        num += w * a.part_o[(row0 + p) * kDV + d];
+        den += w * a.part_ml[(row0 + p) * 2 + 1];
+      }
+      o[d] += coef * (num / den);
+    }
+  }
+  __syncthreads();
+  float r = 1.f;
+  if (a.unit_norm) {
+    float q = 0.f;
+    for (int d = threadIdx.x; d < kDV; d += kThreads) q += o[d] * o[d];
+    r = rsqrtf(block_sum(q, scratch) / static_cast<float>(kDV) + a.eps) * a.post_scale;
+  }
+  for (int d = threadIdx.x; d < kDV; d += kThreads)
+    a.out[static_cast<size_t>(tok) * a.out_stride + head * kDV + d] = from_float<T>(o[d] * r);
+}
+
+// ------------------------------------------------------------------ prompt portions
+constexpr int kBQ = 32, kBK = 32;
+
+template <typename T>
+struct MapsPrefillArgs {
+  const T* q;
+  int q_stride;
+  const T* kcache;
+  const T* vcache;
+  const int32_t* block_table;
+  int max_blocks;
+  const int32_t* tile_seq;
+  const int32_t* tile_tok;
+  const int32_t* tile_rows;
+  const int32_t* positions;
+  T* out;
+  int out_stride;
+  int heads, kv_heads, page_size, tile_quarters;
+  MaskArgs mask;
+  float scale, softcap, lambda, post_scale, eps;
+  int unit_norm;
+};
+
+// Thread t owns query row r = t / 4 and the columns c = t % 4 + 4 i of every tile.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maps_prefill_kernel(const MapsPrefillArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int LDQ = kD + 1;
+  extern __shared__ float smem[];
+  float* Qs = smem;                  // [32][D+1], pre-scaled
+  float* Ks = Qs + kBQ * LDQ;        // [32][D+1]
+  float* Vs = Ks + kBK * LDQ;        // [32][DV]
+  float* Ps = Vs + kBK * kDV;        // [32][33]
+
+  const int tile = blockIdx.x / a.tile_quarters, quarter = blockIdx.x % a.tile_quarters, head = blockIdx.y;
+  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile] + quarter * kBQ;
+  const int rows = min(a.tile_rows[tile] - quarter * kBQ, kBQ);
+  if (rows <= 0) return;
+  const int kvh = head / (a.heads / a.kv_heads);
+  const int pos0 = a.positions[tok0];
+  const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
+  const int r = threadIdx.x >> 2, cq = threadIdx.x & 3;
+  const int my_pos = pos0 + r;
+  const int k_end = pos0 + rows;     // exclusive
+  const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+
+  float o[kDV / 4];
+#pragma unroll
+  for (int i = 0; i < kDV / 4; ++i) o[i] = 0.f;
+
+  for (int m = 0; m < kM; ++m) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBQ * kD; i += kThreads) {
+      const int rr = i / kD, d = i - rr * kD;
+      Qs[rr * LDQ + d] = rr < rows ? to_float(a.q[static_cast<size_t>(tok0 + rr) * a.q_stride +
+                                                  (head * kM + m) * kD + d]) * a.scale
+                                   : 0.f;
+    }
+    float mx = -INFINITY, l = 0.f;
+    float acc[kDV / 4];
+#pragma unroll
+    for (int i = 0; i < kDV / 4; ++i) acc[i] = 0.f;
+
+    for (int k0 = 0; k0 < k_end; k0 += kBK) {
+      // a tile that no row of this CTA sees is skipped: the rows' windows together reach back to
+      // pos0 - window + 1, and the kept first tokens are seen by all
+      const int t_hi = min(k0 + kBK, k_end);
+      if (a.mask.window > 0 && k0 >= a.mask.keep_first && t_hi <= pos0 - a.mask.window + 1) continue;
+      __syncthreads();
+      for (int i = threadIdx.x; i < kBK * kD; i += kThreads) {
+        const int key = i / kD, d = i - key * kD;
+        const int j = k0 + key;
+        float v = 0.f;
+        if (j < k_end) {
+          const size_t page = bt[j / a.page_size];
+          v = to_float(a.kcache[((page * (a.kv_heads * kM) + kvh * kM + m) * a.page_size + j % a.page_size) * kD + d]);
+        }
+        Ks[key * LDQ + d] = v;
+      }
+      for (int i = threadIdx.x; i < kBK * kDV; i += kThreads) {
+        const int key = i / kDV, d = i - key * kDV;
+        const int j = k0 + key;
+        float v = 0.f;
+        if (j < k_end) {
+          const size_t page = bt[j / a.page_size];
+          v = to_float(a.vcache[((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV + d]);
+        }
+        Vs[key * kDV + d] = v;
+      }
+      __syncthreads();
+      float s[kBK / 4];
+#pragma unroll
+      for (int i = 0; i < kBK / 4; ++i) s[i] = 0.f;
+      for (int d = 0; d < kD; ++d) {
+        const float qv = Qs[r * LDQ + d];
+#pragma unroll
+        for (int i = 0; i < kBK / 4; ++i) s[i] += qv * Ks[(cq + 4 * i) * LDQ + d];
+      }
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kBK / 4; ++i) {
+        const int kp = k0 + cq + 4 * i;
+        const bool ok = (r < rows) && key_visible(kp, my_pos, a.mask);
+        float v = s[i];
+        if (a.softcap > 0.f) v = a.softcap * tanhf(v * inv_cap);
+        s[i] = ok ? v : -INFINITY;
+        tmax = fmaxf(tmax, s[i]);
+      }
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      const float m_new = fmaxf(mx, tmax);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (mx == -INFINITY) ? 0.f : expf(mx - m_use);
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kBK / 4; ++i) {
+        const float p = expf(s[i] - m_use);
+        Ps[r * (kBK + 1) + cq + 4 * i] = p;
+        psum += p;
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      l = l * alpha + psum;
+      mx = m_new;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < kDV / 4; ++i) acc[i] *= alpha;
+      for (int c = 0; c < kBK; ++c) {
+        const float p = Ps[r * (kBK + 1) + c];
+#pragma unroll
+        for (int i = 0; i < kDV / 4; ++i) acc[i] += p * Vs[c * kDV + cq + 4 * i];
+      }
+    }
+    const float coef = (m == 0 ? 1.f : -a.lambda) / (l > 0.f ? l : 1.f);
+#pragma unroll
+    for (int i = 0; i < kDV / 4; ++i) o[i] += coef * acc[i];
+  }
+  float scale_out = 1.f;
+  if (a.unit_norm) {
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kDV / 4; ++i) q += o[i] * o[i];
+    q += __shfl_xor_sync(0xffffffffu, q, 1);
+    q += __shfl_xor_sync(0xffffffffu, q, 2);
+    scale_out = rsqrtf(q / static_cast<float>(kDV) + a.eps) * a.post_scale;
+  }
+  if (r < rows) {
+#pragma unroll
+    for (int i = 0; i < kDV / 4; ++i)
+      a.out[static_cast<size_t>(tok0 + r) * a.out_stride + head * kDV + cq + 4 * i] = from_float<T>(o[i] * scale_out);
+  }
+}
+
+template <typename T>
+int launch_maps_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt, int max_blocks,
+                       const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out, int out_stride,
+                       int nitems, int heads, int kv_heads, int page_size, int window, int keep_first, float scale,
+                       float softcap, float lambda, float post_scale, float eps, int unit_norm, cudaStream_t stream) {
+  MapsDecodeArgs<T> a;
+  a.q = static_cast<const T*>(q);
+  a.q_stride = q_stride;
+  a.kcache = static_cast<const T*>(kc);
+  a.vcache = static_cast<const T*>(vc);
+  a.block_table = bt;
+  a.max_blocks = max_blocks;
+  a.items = reinterpret_cast<const int4*>(items);
+  a.part_o = part_o;
+  a.part_ml = part_ml;
+  a.max_parts = max_parts;
+  a.out = static_cast<T*>(out);
+  a.out_stride = out_stride;
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.page_size = page_size;
+  a.mask.window = window;
+  a.mask.keep_first = keep_first;
+  a.scale = scale;
+  a.softcap = softcap;
+  a.lambda = lambda;
+  a.post_scale = post_scale;
+  a.eps = eps;
+  a.unit_norm = unit_norm;
+  cudaError_t e = launch_kernel(maps_decode_kernel<T>, dim3(max_parts, kv_heads, nitems), dim3(kThreads), 0, stream, a);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = launch_kernel(maps_merge_kernel<T>, dim3(nitems, heads), dim3(kThreads), 0, stream, a);
+  return static_cast<int>(e);
+}
+
+template <typename T>
+int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt, int max_blocks,
+                        const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
+                        const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
+                        int kv_heads, int page_size, int window, int keep_first, float scale, float softcap,
+                        float lambda, float post_scale, float eps, int unit_norm, cudaStream_t stream) {
+  MapsPrefillArgs<T> a;
+  a.q = static_cast<const T*>(q);
+  a.q_stride = q_stride;
+  a.kcache = static_cast<const T*>(kc);
+  a.vcache = static_cast<const T*>(vc);
+  a.block_table = bt;
+  a.max_blocks = max_blocks;
+  a.tile_seq = tile_seq;
+  a.tile_tok = tile_tok;
+  a.tile_rows = tile_rows;
+  a.positions = positions;
+  a.out = static_cast<T*>(out);
+  a.out_stride = out_stride;
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.page_size = page_size;
+  a.tile_quarters = (tile_rows_max + kBQ - 1) / kBQ;
+  a.mask.window = window;
+  a.mask.keep_first = keep_first;
+  a.scale = scale;
+  a.softcap = softcap;
+  a.lambda = lambda;
+  a.post_scale = post_scale;
+  a.eps = eps;
+  a.unit_norm = unit_norm;
+  const size_t smem = (kBQ * (kD + 1) + kBK * (kD + 1) + kBK * kDV + kBQ * (kBK + 1)) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    cudaFuncSetAttribute(maps_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    attr_set = true;
+  }
+  return static_cast<int>(launch_kernel(maps_prefill_kernel<T>, dim3(tiles * a.tile_quarters, heads), dim3(kThreads),
+                                        smem, stream, a));
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+extern "C" {
+
+int rl_maps_partition() { return kPart; }
+
+int rl_maps_decode(int dtype, const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
+                   int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out,
+                   int out_stride, int nitems, int heads, int kv_heads, int page_size, int window, int keep_first,
+                   float scale, float softcap, float lambda, float post_scale, float eps, int unit_norm,
+                   cudaStream_t stream) {
+  if (nitems <= 0 || max_parts <= 0) return 0;
+  if (dtype == 0)
+    return launch_maps_decode<float>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, out,
+                                     out_stride, nitems, heads, kv_heads, page_size, window, keep_first, scale, softcap,
+                                     lambda, post_scale, eps, unit_norm, stream);
+  return launch_maps_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, out,
+                                  out_stride, nitems, heads, kv_heads, page_size, window, keep_first, scale, softcap,
+                                  lambda, post_scale, eps, unit_norm, stream);
+}
+
+int rl_maps_prefill(int dtype, const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
+                    int max_blocks, const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
+                    const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
+                    int kv_heads, int page_size, int window, int keep_first, float scale, float softcap, float lambda,
+                    float post_scale, float eps, int unit_norm, cudaStream_t stream) {
+  if (tiles <= 0) return 0;
+  if (dtype == 0)
+    return launch_maps_prefill<float>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
+                                      out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
+                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, stream);
+  return launch_maps_prefill<bf16>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
+                                   out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
+                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, stream);
+}
+
+}  // extern "C"

@@ -74,6 +74,7 @@ struct Core {
   int page_size = 16;
   std::vector<Pool> pools;
   std::vector<int> windows;                    // per group; 0: every key is kept
+  std::vector<int> keep_first;                 // per group: a window never passes the first so many keys
   std::vector<int> free_slots;
   int num_state_slots = 0;
   std::vector<Request> reqs;
@@ -85,6 +86,9 @@ struct Core {
     return &reqs[rid];
   }
   int blocks_for(int tokens) const { return (tokens + page_size - 1) / page_size; }
+  // Blocks [kept_blocks(g), released_upto) of a request are the released ones (none while released_upto
+  // is not beyond kept_blocks): the blocks of the kept first keys stay with the request to its end.
+  int kept_blocks(size_t g) const { return blocks_for(keep_first[g]); }
 };
 
 }  // namespace
@@ -118,12 +122,22 @@ void* rl_hc_create(int num_groups, const int32_t* pages_per_group, const int32_t
   c->page_size = page_size;
   c->pools.resize(num_groups);
   c->windows.assign(windows, windows + num_groups);
+  c->keep_first.assign(num_groups, 0);
   for (int g = 0; g < num_groups; ++g) c->pools[g].init(pages_per_group[g], 1);
   c->num_state_slots = num_state_slots;
   for (int s = num_state_slots - 1; s >= 0; --s) c->free_slots.push_back(s);   // slot 0 first
   return c;
 }
 void rl_hc_destroy(void* h) { delete static_cast<Core*>(h); }
+
+// The first `keys` keys of every sequence stay visible in window group `group`: their pages are not
+// released when the window passes them.  To be called before any request is opened.
+int rl_hc_set_keep_first(void* h, int group, int keys) {
+  Core* c = static_cast<Core*>(h);
+  if (group < 0 || group >= static_cast<int>(c->pools.size()) || keys < 0 || c->num_open > 0) return -1;
+  c->keep_first[group] = keys;
+  return 0;
+}
 
 // A new request: its id (>= 0), or -4 when no state slot is free.
 int rl_hc_open(void* h) {
@@ -156,8 +170,13 @@ int rl_hc_close(void* h, int rid, int* bad) {
   int rc = 0;
   for (size_t g = 0; g < c->pools.size() && rc == 0; ++g) {
     const std::vector<int32_t>& t = r->tables[g];
-    const int from = std::min<int>(r->released_upto[g], static_cast<int>(t.size()));
-    rc = c->pools[g].give_back(t.data() + from, static_cast<int>(t.size()) - from, bad);
+    const int size = static_cast<int>(t.size()), kept = std::min(c->kept_blocks(g), size);
+    int from = 0;
+    if (r->released_upto[g] > kept) {            // the kept first blocks, then what lies behind the released ones
+      rc = c->pools[g].give_back(t.data(), kept, bad);
+      from = std::min(r->released_upto[g], size);
+    }
+    if (rc == 0) rc = c->pools[g].give_back(t.data() + from, size - from, bad);
   }
   c->free_slots.push_back(r->state_slot);
   r->open = false;
@@ -214,9 +233,9 @@ int rl_hc_release_passed(void* h, int rid, int num_computed) {
     const int dead_keys = num_computed - w + 1;               // keys 0 .. dead_keys-1 are dead
     int dead_blocks = std::max(0, dead_keys) / c->page_size;
     dead_blocks = std::min<int>(dead_blocks, static_cast<int>(r->tables[g].size()));
-    if (dead_blocks > r->released_upto[g]) {
+    if (dead_blocks > std::max(r->released_upto[g], c->kept_blocks(g))) {
       std::vector<int32_t>& t = r->tables[g];
-      const int from = r->released_upto[g];
+      const int from = std::max(r->released_upto[g], c->kept_blocks(g));
       int bad = 0;
       const int rc = c->pools[g].give_back(t.data() + from, dead_blocks - from, &bad);
       if (rc < 0) return rc;
@@ -267,7 +286,8 @@ int rl_hc_check(void* h, char* msg, int cap) {
       const Request& r = c->reqs[rid];
       if (!r.open) continue;
       const std::vector<int32_t>& t = r.tables[g];
-      for (int i = r.released_upto[g]; i < static_cast<int>(t.size()); ++i) {
+      for (int i = 0; i < static_cast<int>(t.size()); ++i) {
+        if (i >= c->kept_blocks(g) && i < r.released_upto[g]) continue;      // released
         const int p = t[i];
         if (p < 0 || p >= a.num_pages) {
           std::snprintf(msg, cap, "group %zu: request %zu holds page id %d outside the pool", g, rid, p);

@@ -1,0 +1,468 @@
+// Routed feed-forward (mixture of experts): the router, the grouping of (token, expert) pairs by
+// expert, and the experts' two products as grouped matrix products.
+//
+//   router:   z = W_r x (float32 sums), score = sigmoid(z) (or softmax over the experts); experts lie in
+//             `groups` equal groups of neighbours; a group's score is the sum of its `group_top` best
+//             scores; only experts of the best `keep` groups can be chosen; the `top` best of those are
+//             the token's experts, weighted by their scores (optionally divided by their sum)
+//   pairs:    pair p = token * top + k; `order` lists the pairs expert by expert, `tile_expert` /
+//             `tile_begin` / `tile_rows` cut every expert's pairs into tiles of up to 32 rows
+//   products: up:   act[p, :]  = f(W_up[e]   x[token(p), :])      f = activation
+//             down: y[p, :]    =   W_down[e] act[p, :]
+//   combine:  out[t, :] = sum_k weight[t, k] * y[t * top + k, :] (+ shared[t, :]), k in order
+//
+// A pair's results do not depend on which other pairs share its tile or on the order within the
+// expert's list: every output element is one thread's sum over k in a fixed order.  All sums are float32.
+// bfloat16 operands go through mma.sync (m16n8k16, float32 accumulators); float32 operands through
+// FFMA only.
+#include "common.cuh"
+
+namespace rl {
+
+enum { ACT_NONE = 0, ACT_RELU_SQ = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_GELU_TANH = 4 };
+
+__device__ __forceinline__ float moe_activate(float z, int mode) {
+  switch (mode) {
+    case ACT_RELU_SQ: { const float r = fmaxf(z, 0.f); return r * r; }
+    case ACT_GELU_ERF: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+    case ACT_SILU: return z / (1.f + expf(-z));
+    case ACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    default: return z;
+  }
+}
+
+// ------------------------------------------------------------------ router
+// One warp per token.  Scores live in shared memory (experts floats per warp).  The largest score wins,
+// the lower index among equals.
+struct ArgMax {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgMax warp_argmax(ArgMax a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    const int i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    if (v > a.v || (v == a.v && i < a.i)) {
+      a.v = v;
+      a.i = i;
+    }
+  }
+  return a;
+}
+
+template <typename TA, typename TW>
+__global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __restrict__ router, int tokens,
+                                 int width, int experts, int groups, int keep, int group_top, int top, int softmax,
+                                 int renorm, int32_t* __restrict__ choice, float* __restrict__ weight) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= tokens) return;
+  float* score = sm + warp * (2 * experts + 2 * groups);   // [experts] scores, [experts] working copy, 2 x [groups]
+  float* work = score + experts;
+  float* gscore = work + experts;
+  float* gsel = gscore + groups;
+  const TA* xr = x + static_cast<size_t>(t) * ld;
+  for (int e = 0; e < experts; ++e) {
+    const TW* w = router + static_cast<size_t>(e) * width;
+    float s = 0.f;
+    for (int c = lane; c < width; c += 32) s = fmaf(to_float(xr[c]), to_float(w[c]), s);
+    s = warp_sum(s);
+    if (lane == 0) score[e] = s;
+  }
+  __syncwarp();
+  if (softmax) {
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, score[e]);
+    mx = warp_max(mx);
+    float l = 0.f;
+    for (int e = lane; e < experts; e += 32) l += expf(score[e] - mx);
+    l = warp_sum(l);
+    for (int e = lane; e < experts; e += 32) score[e] = expf(score[e] - mx) / l;
+  } else {
+    for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-score[e]));
+  }
+  __syncwarp();
+  for (int e = lane; e < experts; e += 32) work[e] = score[e];
+  __syncwarp();
+  const int per = experts / groups;
+  if (groups > 1 && keep < groups) {
+    // a group's score: the sum of its group_top best scores
+    for (int g = lane; g < groups; g += 32) {
+      float total = 0.f;
+      int taken_a = -1;                    // (group_top is small: the best, then the best of the rest, ...)
+      float last = INFINITY;
+      for (int k = 0; k < group_top && k < per; ++k) {
+        float best = -INFINITY;
+        int bi = -1;
+        for (int e = 0; e < per; ++e) {
+          const float v = score[g * per + e];
+          // next in the order (value descending, index ascending) after (last, taken_a)
+          const bool after = v < last || (v == last && e > taken_a);
+          if (after && (v > best || bi < 0)) {
+            best = v;
+            bi = e;
+          }
+        }
+        total += best;
+        last = best;
+        taken_a = bi;
+      }
+      gscore[g] = total;
+    }
+    __syncwarp();
+    // the best `keep` groups stay (the lower index among equals); the others' experts cannot be chosen
+    for (int g = lane; g < groups; g += 32) gsel[g] = 0.f;
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      ArgMax a = {-INFINITY, 0x7fffffff};
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gscore[g];
+        if (gsel[g] == 0.f && (a.i == 0x7fffffff || v > a.v)) {
+          a.v = v;
+          a.i = g;
+        }
+      }
+      a = warp_argmax(a);
+      __syncwarp();
+      if (lane == 0 && a.i < groups) gsel[a.i] = 1.f;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gsel[e / per] == 0.f) work[e] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    ArgMax a = {-INFINITY, 0x7fffffff};
+    for (int e = lane; e < experts; e += 32) {
+      const float v = work[e];
+      if (v > a.v || (v == a.v && e < a.i)) {
+        a.v = v;
+        a.i = e;
+      }
+    }
+    a = warp_argmax(a);
+    __syncwarp();
+    const bool found = a.i < experts;              // (false only if fewer experts are allowed than asked for)
+    if (lane == 0) {
+      choice[static_cast<size_t>(t) * top + k] = found ? a.i : 0;
+      weight[static_cast<size_t>(t) * top + k] = found ? score[a.i] : 0.f;
+      if (found) work[a.i] = -INFINITY;
+    }
+    if (found) total += score[a.i];
+    __syncwarp();
+  }
+  if (renorm && lane == 0) {
+    for (int k = 0; k < top; ++k) weight[static_cast<size_t>(t) * top + k] /= total;
+  }
+}
+
+// ------------------------------------------------------------------ pairs grouped by expert
+// One CTA.  counts -> offsets -> order; then the tiles.  meta: [0] number of tiles.
+constexpr int kTileRows = 32;
+
+__global__ void moe_group_kernel(const int32_t* __restrict__ choice, int pairs, int experts,
+                                 int32_t* __restrict__ order, int32_t* __restrict__ tile_expert,
+                                 int32_t* __restrict__ tile_begin, int32_t* __restrict__ tile_rows,
+                                 int32_t* __restrict__ meta) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ int32_t cnt[];          // [experts] counts, then [experts + 1] offsets
+  int32_t* off = cnt + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[choice[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      off[e] = at;
+      for (int r = 0; r < cnt[e]; r += kTileRows) {
+        tile_expert[tiles] = e;
+        tile_begin[tiles] = at + r;
+        tile_rows[tiles] = min(kTileRows, cnt[e] - r);
+        ++tiles;
+      }
+      at += cnt[e];
+    }
+    off[experts] = at;
+    meta[0] = tiles;
+  }
+  __syncthreads();
+  // a pair's place within its expert's list: the pairs of an expert in ascending order (a fixed order,
+  // though no result depends on it)
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  if (pairs <= 4096) {
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+      const int e = choice[p];
+      int before = 0;
+      for (int q = 0; q < p; ++q) before += choice[q] == e;
+      order[off[e] + before] = p;
+    }
+  } else {
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+      const int e = choice[p];
+      order[off[e] + atomicAdd(&cnt[e], 1)] = p;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ grouped products
+// One CTA per (tile of up to 32 pairs of one expert, 64 output features).  Row r of the tile is pair
+// order[begin + r]; its input row is src[pair / src_div] (src_div = top for the first product, whose
+// input is the token's row; 1 for the second, whose input is the pair's own row); its output row is
+// dst[pair].  W is [experts, n, k].
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128)
+moe_gemm_simt_kernel(const TA* __restrict__ src, int ld_src, int src_div, const TW* __restrict__ w, int n, int k,
+                     TA* __restrict__ dst, int ld_dst, const int32_t* __restrict__ order,
+                     const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_begin,
+                     const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ meta, int act) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int BM = kTileRows, BN = 64, BK = 32;
+  __shared__ float As[BM][BK + 1];
+  __shared__ float Ws[BN][BK + 1];
+  __shared__ int32_t pair_of[BM];
+  const int tile = blockIdx.x;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], begin = tile_begin[tile], rows = tile_rows[tile];
+  const int n0 = blockIdx.y * BN;
+  const TW* we = w + static_cast<size_t>(e) * n * k;
+  if (threadIdx.x < BM) pair_of[threadIdx.x] = threadIdx.x < rows ? order[begin + threadIdx.x] : -1;
+  __syncthreads();
+  // thread (ty, tx): rows ty * 4 .. + 3 (8 groups), columns tx, tx + 16, tx + 32, tx + 48
+  const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < BM * BK; i += 128) {
+      const int r = i / BK, c = i - r * BK;
+      const int p = pair_of[r];
+      As[r][c] = (p >= 0 && k0 + c < k) ? to_float(src[static_cast<size_t>(p / src_div) * ld_src + k0 + c]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < BN * BK; i += 128) {
+      const int r = i / BK, c = i - r * BK;
+      Ws[r][c] = (n0 + r < n && k0 + c < k) ? to_float(we[static_cast<size_t>(n0 + r) * k + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int c = 0; c < BK; ++c) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[ty * 4 + i][c];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wv[j] = Ws[tx + 16 * j][c];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = pair_of[ty * 4 + i];
+    if (p < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = n0 + tx + 16 * j;
+      if (col < n) dst[static_cast<size_t>(p) * ld_dst + col] = from_float<TA>(moe_activate(acc[i][j], act));
+    }
+  }
+}
+
+// The same tile on the tensor cores for bfloat16: four warps, each 16 of the 64 output features as two
+// n-tiles of 8, over both 16-row halves of the tile; A (pairs' rows) and W tiles staged in shared memory
+// as bfloat16.  mma.sync.m16n8k16, float32 accumulators, k in ascending blocks of 32.
+__device__ __forceinline__ void mma_bf16_16816(float* d, const uint32_t* a, const uint32_t* b) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ src, int ld_src, int src_div, const bf16* __restrict__ w, int n, int k,
+                    bf16* __restrict__ dst, int ld_dst, const int32_t* __restrict__ order,
+                    const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_begin,
+                    const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ meta, int act) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int BM = kTileRows, BN = 64, BK = 32, LD = BK + 8;      // 80-byte rows: fragment reads hit distinct banks
+  __shared__ __align__(16) bf16 As[BM][LD];
+  __shared__ __align__(16) bf16 Ws[BN][LD];
+  __shared__ int32_t pair_of[BM];
+  const int tile = blockIdx.x;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], begin = tile_begin[tile], rows = tile_rows[tile];
+  const int n0 = blockIdx.y * BN;
+  const bf16* we = w + static_cast<size_t>(e) * n * k;
+  if (threadIdx.x < BM) pair_of[threadIdx.x] = threadIdx.x < rows ? order[begin + threadIdx.x] : -1;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  float acc[2][2][4];               // [row half][n tile][fragment]
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) acc[i][j][f] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    __syncthreads();
+    // 16-byte pieces: a row of 32 elements is four pieces (k is a multiple of 8)
+    for (int i = threadIdx.x; i < BM * 4; i += 128) {
+      const int r = i >> 2, c = (i & 3) * 8;
+      const int p = pair_of[r];
+      uint4 v = zero;
+      if (p >= 0 && k0 + c < k) v = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(p / src_div) * ld_src + k0 + c);
+      *reinterpret_cast<uint4*>(&As[r][c]) = v;
+    }
+    for (int i = threadIdx.x; i < BN * 4; i += 128) {
+      const int r = i >> 2, c = (i & 3) * 8;
+      uint4 v = zero;
+      if (n0 + r < n && k0 + c < k) v = *reinterpret_cast<const uint4*>(we + static_cast<size_t>(n0 + r) * k + k0 + c);
+      *reinterpret_cast<uint4*>(&Ws[r][c]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t b[2][2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const bf16* wr = &Ws[warp * 16 + j * 8 + gid][kk + tig * 2];
+        b[j][0] = *reinterpret_cast<const uint32_t*>(wr);
+        b[j][1] = *reinterpret_cast<const uint32_t*>(wr + 8);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        uint32_t a[4];
+        const bf16* ar = &As[i * 16 + gid][kk + tig * 2];
+        a[0] = *reinterpret_cast<const uint32_t*>(ar);
+        a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * LD);
+        a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * LD + 8);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) mma_bf16_16816(acc[i][j], a, b[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int p = pair_of[i * 16 + gid + half * 8];
+      if (p < 0) continue;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int col = n0 + warp * 16 + j * 8 + tig * 2;
+        const float v0 = moe_activate(acc[i][j][half * 2], act), v1 = moe_activate(acc[i][j][half * 2 + 1], act);
+        bf16* d = dst + static_cast<size_t>(p) * ld_dst + col;
+        if (col + 1 < n && (ld_dst % 2 == 0)) {
+          *reinterpret_cast<__nv_bfloat162*>(d) = __floats2bfloat162_rn(v0, v1);
+        } else {
+          if (col < n) d[0] = __float2bfloat16_rn(v0);
+          if (col + 1 < n) d[1] = __float2bfloat16_rn(v1);
+        }
+      }
+    }
+}
+
+// ------------------------------------------------------------------ combine
+// out[t, c] = sum_k weight[t, k] * y[t * top + k, c] (+ shared[t, c])
+template <typename TA>
+__global__ void moe_combine_kernel(const TA* __restrict__ y, const float* __restrict__ weight,
+                                   const TA* __restrict__ shared, TA* __restrict__ out, int width, int top) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.y;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < top; ++k)
+      s = fmaf(weight[static_cast<size_t>(t) * top + k], to_float(y[(static_cast<size_t>(t) * top + k) * width + c]), s);
+    if (shared != nullptr) s += to_float(shared[static_cast<size_t>(t) * width + c]);
+    out[static_cast<size_t>(t) * width + c] = from_float<TA>(s);
+  }
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+extern "C" {
+
+int rl_moe_tile_rows() { return kTileRows; }
+
+int rl_moe_route(const void* x, int act_dtype, int ld, const void* router, int w_dtype, int tokens, int width,
+                 int experts, int groups, int keep, int group_top, int top, int softmax, int renorm, int32_t* choice,
+                 float* weight, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * (2 * experts + 2 * groups) * sizeof(float);
+  dim3 grid((tokens + warps - 1) / warps), block(warps * 32);
+#define RL_CASE(TA, TW)                                                                                            \
+  launch_kernel(moe_route_kernel<TA, TW>, grid, block, smem, stream, static_cast<const TA*>(x), ld,                \
+                static_cast<const TW*>(router), tokens, width, experts, groups, keep, group_top, top, softmax,     \
+                renorm, choice, weight)
+  if (act_dtype == 0) RL_CASE(float, float);
+  else if (w_dtype == 0) RL_CASE(bf16, float);
+  else RL_CASE(bf16, bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_moe_group(const int32_t* choice, int pairs, int experts, int32_t* order, int32_t* tile_expert,
+                 int32_t* tile_begin, int32_t* tile_rows, int32_t* meta, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  launch_kernel(moe_group_kernel, dim3(1), dim3(256), (2 * experts + 1) * sizeof(int32_t), stream, choice, pairs,
+                experts, order, tile_expert, tile_begin, tile_rows, meta);
+  RL_LAUNCH_END();
+}
+
+// max_tiles: the most tiles the grouping can have made (pairs / 32 + experts); CTAs beyond the real
+// number leave at once.
+int rl_moe_gemm(int act_dtype, const void* src, int ld_src, int src_div, const void* w, int n, int k, void* dst,
+                int ld_dst, const int32_t* order, const int32_t* tile_expert, const int32_t* tile_begin,
+                const int32_t* tile_rows, const int32_t* meta, int max_tiles, int act, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  dim3 grid(max_tiles, (n + 63) / 64);
+  if (act_dtype == 0) {
+    launch_kernel(moe_gemm_simt_kernel<float, float>, grid, dim3(128), 0, stream, static_cast<const float*>(src),
+                  ld_src, src_div, static_cast<const float*>(w), n, k, static_cast<float*>(dst), ld_dst, order,
+                  tile_expert, tile_begin, tile_rows, meta, act);
+  } else if (k % 8 == 0 && ld_src % 8 == 0 && (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
+             (reinterpret_cast<uintptr_t>(w) % 16 == 0)) {
+    launch_kernel(moe_gemm_mma_kernel, grid, dim3(128), 0, stream, static_cast<const bf16*>(src), ld_src, src_div,
+                  static_cast<const bf16*>(w), n, k, static_cast<bf16*>(dst), ld_dst, order, tile_expert, tile_begin,
+                  tile_rows, meta, act);
+  } else {
+    launch_kernel(moe_gemm_simt_kernel<bf16, bf16>, grid, dim3(128), 0, stream, static_cast<const bf16*>(src), ld_src,
+                  src_div, static_cast<const bf16*>(w), n, k, static_cast<bf16*>(dst), ld_dst, order, tile_expert,
+                  tile_begin, tile_rows, meta, act);
+  }
+  RL_LAUNCH_END();
+}
+
+int rl_moe_combine(int act_dtype, const void* y, const float* weight, const void* shared, void* out, int tokens,
+                   int width, int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  dim3 grid(min((width + 255) / 256, 32), tokens);
+  if (act_dtype == 0)
+    launch_kernel(moe_combine_kernel<float>, grid, dim3(256), 0, stream, static_cast<const float*>(y), weight,
+                  static_cast<const float*>(shared), static_cast<float*>(out), width, top);
+  else
+    launch_kernel(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, static_cast<const bf16*>(y), weight,
+                  static_cast<const bf16*>(shared), static_cast<bf16*>(out), width, top);
+  RL_LAUNCH_END();
+}
+
+}  // extern "C"

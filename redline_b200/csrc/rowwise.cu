@@ -1,0 +1,215 @@
+// Row-wise kernels for blocks that norm a sublayer's input AND its output: layer norm (weight, no
+// bias) fused with the add to the float32 residual stream and with the norm that follows; bias +
+// activation over a range of columns; the write of any per-token tensor into its paged cache; and
+// the gated unit-RMS norm that closes a linear-attention mixer.
+//
+// Activations are float or bfloat16; means, variances, the stream and the activations'
+// arithmetic are float.  The variance is the mean of squared deviations (two passes over a row
+// held in shared memory), not E[x^2] - E[x]^2.
+#include "common.cuh"
+
+namespace rl {
+
+enum { ACT_NONE = 0, ACT_RELU_SQ = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_GELU_TANH = 4, ACT_SIGMOID = 5 };
+
+__device__ __forceinline__ float activate(float z, int mode) {
+  switch (mode) {
+    case ACT_RELU_SQ: { const float r = fmaxf(z, 0.f); return r * r; }
+    case ACT_GELU_ERF: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+    case ACT_SILU: return z / (1.f + expf(-z));
+    case ACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    case ACT_SIGMOID: return 1.f / (1.f + expf(-z));
+    default: return z;
+  }
+}
+
+// ------------------------------------------------ residual += LN(delta) * post_w;  out = LN(residual) * pre_w
+// One CTA per row; the row lives in dynamic shared memory (hidden floats).
+//   delta / post_w given:  the sublayer's output is normed and added to the stream (written back)
+//   delta without post_w:  the sublayer's output is added as it is
+//   out / pre_w given:     the (new) stream row is normed for the next sublayer
+//   rows_idx given:        out row i comes from stream row rows_idx[i]; nothing is added (delta is null)
+// kind: 0 layer norm (mean removed), 1 RMS norm; both with a weight and without a bias.
+template <typename TA, typename TW>
+__global__ void sandwich_norm_kernel(float* __restrict__ residual, const TA* __restrict__ delta, int ld_delta,
+                                     const TW* __restrict__ post_w, const TW* __restrict__ pre_w,
+                                     TA* __restrict__ out, int ld_out, const int32_t* __restrict__ rows_idx,
+                                     int hidden, float eps, int kind) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows_idx ? rows_idx[r] : r;
+  float* res = residual + static_cast<size_t>(src) * hidden;
+  const float inv_n = 1.f / static_cast<float>(hidden);
+  if (delta != nullptr && post_w == nullptr) {
+    const TA* d = delta + static_cast<size_t>(src) * ld_delta;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = res[c] + to_float(d[c]);
+      res[c] = v;
+      row[c] = v;
+    }
+  } else if (delta != nullptr) {
+    const TA* d = delta + static_cast<size_t>(src) * ld_delta;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = to_float(d[c]);
+      row[c] = v;
+      s += v;
+    }
+    const float mean = kind == 0 ? block_sum(s, scratch) * inv_n : 0.f;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = row[c] - mean;
+      q += v * v;
+    }
+    const float rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = res[c] + (row[c] - mean) * rstd * to_float(post_w[c]);
+      res[c] = v;
+      row[c] = v;
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row[c] = res[c];
+  }
+  if (out == nullptr) return;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) s += row[c];
+  const float mean = kind == 0 ? block_sum(s, scratch) * inv_n : 0.f;
+  float q = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = row[c] - mean;
+    q += v * v;
+  }
+  const float rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+  TA* o = out + static_cast<size_t>(r) * ld_out;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    o[c] = from_float<TA>((row[c] - mean) * rstd * to_float(pre_w[c]));
+}
+
+// ------------------------------------------------ x[r, c] = act(x[r, c] + bias[c]) for c < cols
+template <typename TA>
+__global__ void bias_act_kernel(TA* __restrict__ x, int ld, const float* __restrict__ bias, int cols, int mode) {
+  pdl_launch();
+  pdl_wait();
+  TA* p = x + static_cast<size_t>(blockIdx.y) * ld;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
+    float v = to_float(p[c]);
+    if (bias != nullptr) v = to_float(from_float<TA>(v + bias[c]));   // (the biased projection is what is stored)
+    p[c] = from_float<TA>(activate(v, mode));
+  }
+}
+
+// ------------------------------------------------ cache[page, head, offset, :] = src[t, col + head * dim : ...]
+// `cache` is [pages, heads, page_size, dim]; slots[t] = page * page_size + offset, negative: no write;
+// a slot beyond the pool is not written and sets bit 2 of *status.
+template <typename TA>
+__global__ void cache_store_kernel(const TA* __restrict__ src, int ld, int col, int heads, int dim,
+                                   const int32_t* __restrict__ slots, TA* __restrict__ cache, int page_size,
+                                   long long num_slots, int* status) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(status, 4);
+    return;
+  }
+  const size_t page = slot / page_size, off = slot % page_size;
+  const TA* s = src + static_cast<size_t>(t) * ld + col;
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+    const int h = i / dim, d = i - h * dim;
+    cache[((page * heads + h) * page_size + off) * dim + d] = s[i];
+  }
+}
+
+// ------------------------------------------------ out = o / rms(o) * w * sigmoid(gate)
+// o is the float32 output of a recurrence [T, n]; gate lies in a projection buffer (row stride ld_gate).
+template <typename TA, typename TW>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const TA* __restrict__ gate, int ld_gate,
+                                     const TW* __restrict__ w, TA* __restrict__ out, int n, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float* orow = o + static_cast<size_t>(r) * n;
+  float q = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) q += orow[c] * orow[c];
+  const float rstd = rsqrtf(block_sum(q, scratch) / static_cast<float>(n) + eps);
+  const TA* g = gate + static_cast<size_t>(r) * ld_gate;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float s = 1.f / (1.f + expf(-to_float(g[c])));
+    out[static_cast<size_t>(r) * n + c] = from_float<TA>(orow[c] * rstd * to_float(w[c]) * s);
+  }
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+extern "C" {
+
+enum { RL_F32 = 0, RL_BF16 = 1 };
+
+int rl_sandwich_norm(float* residual, const void* delta, int ld_delta, const void* post_w, const void* pre_w,
+                     int w_dtype, void* out, int ld_out, int act_dtype, const int32_t* rows_idx, int rows, int hidden,
+                     float eps, int kind, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int th = hidden >= 2048 ? 512 : 256;
+  const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+#define RL_CASE(TA, TW)                                                                                          \
+  do {                                                                                                           \
+    if (smem > 48 * 1024)                                                                                        \
+      cudaFuncSetAttribute(sandwich_norm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_kernel(sandwich_norm_kernel<TA, TW>, dim3(rows), dim3(th), smem, stream, residual,                    \
+                  static_cast<const TA*>(delta), ld_delta, static_cast<const TW*>(post_w),                       \
+                  static_cast<const TW*>(pre_w), static_cast<TA*>(out), ld_out, rows_idx, hidden, eps, kind);    \
+  } while (0)
+  if (act_dtype == RL_F32) RL_CASE(float, float);
+  else if (w_dtype == RL_F32) RL_CASE(bf16, float);
+  else RL_CASE(bf16, bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_bias_act(void* x, int act_dtype, int ld, const float* bias, int rows, int cols, int mode, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int th = 256;
+  dim3 grid(min((cols + th - 1) / th, 64), rows);
+  if (act_dtype == RL_F32)
+    launch_kernel(bias_act_kernel<float>, grid, dim3(th), 0, stream, static_cast<float*>(x), ld, bias, cols, mode);
+  else
+    launch_kernel(bias_act_kernel<bf16>, grid, dim3(th), 0, stream, static_cast<bf16*>(x), ld, bias, cols, mode);
+  RL_LAUNCH_END();
+}
+
+int rl_cache_store(const void* src, int act_dtype, int ld, int col, int heads, int dim, const int32_t* slots,
+                   void* cache, int page_size, long long num_slots, int tokens, int* status, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int th = heads * dim >= 256 ? 256 : 128;
+  if (act_dtype == RL_F32)
+    launch_kernel(cache_store_kernel<float>, dim3(tokens), dim3(th), 0, stream, static_cast<const float*>(src), ld,
+                  col, heads, dim, slots, static_cast<float*>(cache), page_size, num_slots, status);
+  else
+    launch_kernel(cache_store_kernel<bf16>, dim3(tokens), dim3(th), 0, stream, static_cast<const bf16*>(src), ld,
+                  col, heads, dim, slots, static_cast<bf16*>(cache), page_size, num_slots, status);
+  RL_LAUNCH_END();
+}
+
+int rl_gated_rmsnorm(const float* o, const void* gate, int ld_gate, const void* w, int w_dtype, void* out,
+                     int act_dtype, int rows, int n, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int th = 256;
+#define RL_CASE(TA, TW)                                                                                        \
+  launch_kernel(gated_rmsnorm_kernel<TA, TW>, dim3(rows), dim3(th), 0, stream, o, static_cast<const TA*>(gate), \
+                ld_gate, static_cast<const TW*>(w), static_cast<TA*>(out), n, eps)
+  if (act_dtype == RL_F32) RL_CASE(float, float);
+  else if (w_dtype == RL_F32) RL_CASE(bf16, float);
+  else RL_CASE(bf16, bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+}  // extern "C"

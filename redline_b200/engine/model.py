@@ -31,6 +31,14 @@ class DecoderModel:
             self.blocks.append(block_cls(build_part("norm", ls.mixer_norm, rt), build_part("mixer", ls.mixer, rt),
                                          build_part("norm", ls.ffn_norm, rt) if ls.ffn_norm is not None else None,
                                          build_part("ffn", ls.ffn, rt) if ls.ffn is not None else None, rt))
+            if ls.mixer_post_norm is not None or ls.ffn_post_norm is not None:
+                block = self.blocks[-1]
+                if not hasattr(block, "mixer_post_norm"):
+                    raise ValueError(f"the block arrangement '{ls.arrangement}' takes no norms of a sublayer's output")
+                if ls.mixer_post_norm is None or (ls.ffn is not None) != (ls.ffn_post_norm is not None):
+                    raise ValueError("a layer with output norms has one for every sublayer")
+                block.mixer_post_norm = build_part("norm", ls.mixer_post_norm, rt)
+                block.ffn_post_norm = build_part("norm", ls.ffn_post_norm, rt) if ls.ffn_post_norm is not None else None
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.nvtx_layers = False           # one NVTX range per layer call (set by the runner from the engine's options)

@@ -562,6 +562,249 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
              _ptr(tc_status(q.device)), _stream()), "attn_prefill")
 
 
+# ------------------------------------------- row-wise kernels of blocks with norms on both sides
+
+ACT_NONE, ACT_RELU_SQ, ACT_GELU_ERF, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID = 0, 1, 2, 3, 4, 5
+ACTIVATIONS = {"none": ACT_NONE, "relu_squared": ACT_RELU_SQ, "gelu": ACT_GELU_ERF, "silu": ACT_SILU,
+               "gelu_tanh": ACT_GELU_TANH}
+NORM_LAYER, NORM_RMS = 0, 1
+
+
+def _rw() -> ctypes.CDLL:
+    return _lib("rowwise", "rowwise.cu")
+
+
+def sandwich_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_w: Optional[torch.Tensor],
+                  pre_w: Optional[torch.Tensor], out: Optional[torch.Tensor], eps: float, kind: int = NORM_LAYER,
+                  rows_idx: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
+    """residual (float32 stream) += norm(delta) * post_w (delta given; without post_w delta is added as it
+    is), then out = norm(residual) * pre_w (out given).  ``kind``: layer norm (mean removed, variance as the
+    mean of squared deviations) or RMS norm, both with a weight and no bias.  With ``rows_idx`` out row i
+    comes from stream row rows_idx[i] and nothing is added."""
+    _need_cuda(residual, delta, out)
+    n = rows if rows is not None else (rows_idx.numel() if rows_idx is not None else residual.shape[0])
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise KernelError("sandwich_norm: the stream must be contiguous float32")
+    if rows_idx is not None and delta is not None:
+        raise KernelError("sandwich_norm: gathered rows take no addend")
+    act = out if out is not None else delta
+    if act is None:
+        return
+    ws = [w for w in (post_w, pre_w) if w is not None]
+    if (out is not None and pre_w is None) or any(w.dtype != ws[0].dtype for w in ws):
+        raise KernelError("sandwich_norm: an output needs its weight, and the weights one type")
+    if delta is not None and out is not None and delta.dtype != out.dtype:
+        raise KernelError("sandwich_norm: delta and out must have the same dtype")
+    f = _fn(_rw(), "rl_sandwich_norm", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                         c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), delta.stride(0) if delta is not None else 0, _ptr(post_w), _ptr(pre_w),
+             _code(ws[0].dtype) if ws else 0, _ptr(out), out.stride(0) if out is not None else 0, _code(act.dtype),
+             _ptr(rows_idx), n, residual.shape[-1], float(eps), kind, _stream()), "sandwich_norm")
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], act: int, cols: Optional[int] = None,
+             rows: Optional[int] = None) -> None:
+    """In place: x[r, c] = act(x[r, c] + bias[c]) for c < cols (x may be a row-strided view; bias float32)."""
+    _need_cuda(x, bias)
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous()):
+        raise KernelError("bias_act: the bias must be contiguous float32")
+    if x.stride(1) != 1:
+        raise KernelError("bias_act: rows must be contiguous")
+    f = _fn(_rw(), "rl_bias_act", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(bias), rows if rows is not None else x.shape[0],
+             cols if cols is not None else x.shape[1], act, _stream()), "bias_act")
+
+
+def cache_store(src: torch.Tensor, col: int, heads: int, dim: int, slots: torch.Tensor, cache: torch.Tensor,
+                page_size: int, status: torch.Tensor, tokens: Optional[int] = None) -> None:
+    """cache [pages, heads, page_size, dim] <- columns [col, col + heads * dim) of src's rows, each token at
+    its slot (page * page_size + offset; negative: not written; beyond the pool: bit 2 of ``status``)."""
+    _need_cuda(src, slots, cache)
+    if src.dtype != cache.dtype or src.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("cache_store: source and cache must have one type, contiguous rows")
+    f = _fn(_rw(), "rl_cache_store", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                       c_longlong, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(src), _code(src.dtype), src.stride(0), col, heads, dim, _ptr(slots), _ptr(cache), page_size,
+             cache.shape[0] * page_size, tokens if tokens is not None else src.shape[0], _ptr(status), _stream()),
+           "cache_store")
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+                  rows: Optional[int] = None) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate): o float32 [T, n] contiguous, gate a
+    (row-strided) view [T, n] of the activation type."""
+    _need_cuda(o, gate, weight, out)
+    if o.dtype != torch.float32 or not o.is_contiguous() or gate.stride(1) != 1 or not out.is_contiguous() \
+            or gate.dtype != out.dtype:
+        raise KernelError("gated_rmsnorm: o float32 contiguous, gate and out of the activation type")
+    f = _fn(_rw(), "rl_gated_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                         c_float, c_void_p])
+    _check(f(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _code(weight.dtype), _ptr(out), _code(out.dtype),
+             rows if rows is not None else o.shape[0], o.shape[1], float(eps), _stream()), "gated_rmsnorm")
+
+
+# ------------------------------------ attention with score maps, a capped score and kept first tokens
+
+def _maps(dim: int, vdim: int, maps: int) -> ctypes.CDLL:
+    if not (1 <= dim <= 256 and 4 <= vdim <= 256 and vdim % 4 == 0 and maps in (1, 2)):
+        raise KernelError(f"attention_maps takes key sizes up to 256, value sizes that are multiples of 4 up to 256 "
+                          f"and one or two maps; got {dim}, {vdim}, {maps}")
+    return _lib(f"attention_maps_d{dim}_v{vdim}_m{maps}", "attention_maps.cu",
+                {"RL_QK_DIM": dim, "RL_V_DIM": vdim, "RL_MAPS": maps})
+
+
+def maps_attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                     block_table: torch.Tensor, items: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                     max_parts: int, out: torch.Tensor, nitems: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                     maps: int, page_size: int, window: int, keep_first: int, scale: float, softcap: float,
+                     lam: float, post_scale: float, eps: float, unit_norm: bool) -> None:
+    """One query token per item (``items`` as for ``attn_decode``) over the paged cache, ``maps`` score maps
+    per head over shared values (csrc/attention_maps.cu): q rows (head, map) of ``dim``, key cache
+    [pages, kv_heads * maps, page, dim], value cache [pages, kv_heads, page, vdim], out heads of ``vdim``."""
+    _need_cuda(q, kcache, vcache, out)
+    f = _fn(_maps(dim, vdim, maps), "rl_maps_decode",
+            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_int,
+             c_void_p])
+    need = nitems * heads * maps * max_parts
+    if part_o.numel() < need * vdim or part_ml.numel() < need * 2:
+        raise KernelError("maps_attn_decode: partition workspace too small")
+    if items.data_ptr() % 16 != 0:
+        raise KernelError("maps_attn_decode: items must be 16-byte aligned")
+    _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
+             _ptr(items), _ptr(part_o), _ptr(part_ml), max_parts, _ptr(out), out.stride(0), nitems, heads, kv_heads,
+             page_size, window, keep_first, float(scale), float(softcap), float(lam), float(post_scale), float(eps),
+             1 if unit_norm else 0, _stream()), "maps_attn_decode", 2)
+
+
+def maps_attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                      block_table: torch.Tensor, tile_seq: torch.Tensor, tile_tok: torch.Tensor,
+                      tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,
+                      tile_rows_max: int, heads: int, kv_heads: int, dim: int, vdim: int, maps: int, page_size: int,
+                      window: int, keep_first: int, scale: float, softcap: float, lam: float, post_scale: float,
+                      eps: float, unit_norm: bool) -> None:
+    """Tiles of up to ``tile_rows_max`` consecutive query tokens of one sequence; otherwise as
+    ``maps_attn_decode``."""
+    _need_cuda(q, kcache, vcache, out)
+    f = _fn(_maps(dim, vdim, maps), "rl_maps_prefill",
+            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
+             c_float, c_int, c_void_p])
+    _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
+             _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions), _ptr(out), out.stride(0), tiles,
+             tile_rows_max, heads, kv_heads, page_size, window, keep_first, float(scale), float(softcap), float(lam),
+             float(post_scale), float(eps), 1 if unit_norm else 0, _stream()), "maps_attn_prefill")
+
+
+# ------------------------------------------------------- linear attention with a decaying state
+
+LINEAR_ATTN_CHUNK_FROM = 256       # sequences that bring at least so many tokens are cut into chunks
+LINEAR_ATTN_MAX_CHUNKS = 64
+
+
+def linear_attention_chunks(longest: int) -> Tuple[int, int]:
+    """(chunk length, most chunks) for a step whose longest sequence brings ``longest`` tokens; (0, 1) when
+    every sequence is run as one chain."""
+    if longest < LINEAR_ATTN_CHUNK_FROM:
+        return 0, 1
+    chunk = max(64, (longest + LINEAR_ATTN_MAX_CHUNKS - 1) // LINEAR_ATTN_MAX_CHUNKS)
+    return chunk, (longest + chunk - 1) // chunk
+
+
+def linear_attention(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, seq_of_token: torch.Tensor,
+                     state_slot: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                     tokens: int, sequences: int, heads: int, dim: int, vdim: int,
+                     chunk_state: Optional[torch.Tensor] = None, chunk: int = 0, max_chunks: int = 1) -> None:
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head over every sequence of the step, from and
+    into the sequences' state slots (csrc/linear_attention.cu).  qkv [tokens, *] holds q, k (heads x dim)
+    and v (heads x vdim) at the given columns; state float32 [slots, heads, dim, vdim]; out float32
+    [tokens, heads * vdim].  With ``chunk_state`` (float32, sequences * max_chunks * heads * dim * vdim)
+    sequences are cut into chunks of ``chunk`` tokens that run side by side."""
+    _need_cuda(qkv, state, out)
+    if state.dtype != torch.float32 or out.dtype != torch.float32 or decay.dtype != torch.float32 \
+            or not state.is_contiguous() or not out.is_contiguous() or qkv.stride(1) != 1:
+        raise KernelError("linear_attention: state, decay and out are contiguous float32")
+    if not 1 <= dim <= 256:
+        raise KernelError(f"linear_attention takes key sizes up to 256; got {dim}")
+    if chunk_state is not None and max_chunks > 1 and \
+            chunk_state.numel() < sequences * max_chunks * heads * dim * vdim:
+        raise KernelError("linear_attention: chunk workspace too small")
+    f = _fn(_lib(f"linear_attention_d{dim}", "linear_attention.cu", {"RL_LIN_DIM": dim}), "rl_linear_attention",
+            [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    chunked = chunk_state is not None and max_chunks > 1
+    _check(f(_code(qkv.dtype), _ptr(qkv), qkv.stride(0), q_col, k_col, v_col, _ptr(seq_of_token), _ptr(state_slot),
+             _ptr(decay), _ptr(state), _ptr(out), _ptr(chunk_state) if chunked else None, tokens, sequences, heads,
+             vdim, chunk, max_chunks if chunked else 1, _stream()), "linear_attention", 3 if chunked else 1)
+
+
+# ------------------------------------------------------------------- routed feed-forward
+
+def _moe() -> ctypes.CDLL:
+    return _lib("moe", "moe.cu")
+
+
+MOE_TILE_ROWS = 32
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    return pairs // MOE_TILE_ROWS + experts
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, choice: torch.Tensor, weight: torch.Tensor, tokens: int,
+              groups: int, keep: int, group_top: int, top: int, softmax: bool = False, renorm: bool = False) -> None:
+    """Per token: scores of the experts (float32 sums; sigmoid, or softmax), the best ``keep`` of ``groups``
+    groups of neighbouring experts by the sum of their ``group_top`` best scores, the ``top`` best experts
+    of those into choice [tokens, top] int32 with their scores in weight [tokens, top] float32."""
+    _need_cuda(x, router, choice, weight)
+    experts, width = router.shape
+    if experts % max(groups, 1) != 0 or choice.dtype != torch.int32 or weight.dtype != torch.float32 \
+            or x.stride(1) != 1 or not router.is_contiguous():
+        raise KernelError("moe_route: experts must divide into the groups; choice int32, weight float32")
+    f = _fn(_moe(), "rl_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(router), _code(router.dtype), tokens, width, experts,
+             max(groups, 1), keep, group_top, top, 1 if softmax else 0, 1 if renorm else 0, _ptr(choice), _ptr(weight),
+             _stream()), "moe_route")
+
+
+def moe_group(choice: torch.Tensor, pairs: int, experts: int, order: torch.Tensor, tile_expert: torch.Tensor,
+              tile_begin: torch.Tensor, tile_rows: torch.Tensor, meta: torch.Tensor) -> None:
+    """Lists the (token, slot) pairs expert by expert (``order``) and cuts every expert's list into tiles of
+    up to 32 pairs (``tile_*``, their number in meta[0]); all int32, the tile lists ``moe_max_tiles`` long."""
+    _need_cuda(choice, order, tile_expert, tile_begin, tile_rows, meta)
+    f = _fn(_moe(), "rl_moe_group", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(choice), pairs, experts, _ptr(order), _ptr(tile_expert), _ptr(tile_begin), _ptr(tile_rows),
+             _ptr(meta), _stream()), "moe_group")
+
+
+def moe_gemm(src: torch.Tensor, src_div: int, w: torch.Tensor, dst: torch.Tensor, order: torch.Tensor,
+             tile_expert: torch.Tensor, tile_begin: torch.Tensor, tile_rows: torch.Tensor, meta: torch.Tensor,
+             max_tiles: int, act: int = ACT_NONE) -> None:
+    """dst[pair] = act(w[expert of the pair] @ src[pair // src_div]) for every listed pair: w [experts, n, k]
+    (or [experts * n, k]) with ``n = dst.shape[1]``, src [*, k], dst [pairs, n]."""
+    _need_cuda(src, w, dst)
+    n, k = dst.shape[1], src.shape[1]
+    if w.shape[-1] != k or not w.is_contiguous() or src.stride(1) != 1 or dst.stride(1) != 1 or src.dtype != dst.dtype \
+            or w.dtype != src.dtype:
+        raise KernelError(f"moe_gemm: shapes src{tuple(src.shape)} w{tuple(w.shape)} dst{tuple(dst.shape)}, one type")
+    f = _fn(_moe(), "rl_moe_gemm", [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_code(src.dtype), _ptr(src), src.stride(0), src_div, _ptr(w), n, k, _ptr(dst), dst.stride(0), _ptr(order),
+             _ptr(tile_expert), _ptr(tile_begin), _ptr(tile_rows), _ptr(meta), max_tiles, act, _stream()), "moe_gemm")
+
+
+def moe_combine(y: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor,
+                tokens: int, top: int) -> None:
+    """out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]), k in order; y, shared and out contiguous."""
+    _need_cuda(y, weight, out)
+    if not (y.is_contiguous() and out.is_contiguous() and (shared is None or shared.is_contiguous())):
+        raise KernelError("moe_combine: contiguous tensors")
+    f = _fn(_moe(), "rl_moe_combine", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_code(out.dtype), _ptr(y), _ptr(weight), _ptr(shared), _ptr(out), tokens, out.shape[1], top, _stream()),
+           "moe_combine")
+
+
 # -------------------------------------------------------------------- sampling
 
 SAMPLE_CHUNKS = 64
@@ -604,6 +847,8 @@ def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
         build.compile_module("gemm_tc", "gemm_tc.cu", verbose=verbose),
         build.compile_module("gemm_mid", "gemm_mid.cu", verbose=verbose),
         build.compile_module("sampling", "sampling.cu", verbose=verbose),
+        build.compile_module("rowwise", "rowwise.cu", verbose=verbose),
+        build.compile_module("moe", "moe.cu", verbose=verbose),
         build.compile_module("host_core", "host_core.cpp", verbose=verbose),   # host-only: cache manager, batch filler
     ]
     for d in head_dims:

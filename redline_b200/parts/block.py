@@ -68,3 +68,37 @@ class PreNormBlock(Block):
         if delta is not None:
             n += delta.numel() * delta.element_size()
         return float(n)
+
+
+@register("block", "sandwich")
+class SandwichBlock(Block):
+    """h += norm_1b(mixer(norm_1(h))); h += norm_2b(ffn(norm_2(h))): every sublayer's input AND output is
+    normed.  ``mixer_post_norm`` / ``ffn_post_norm`` are set by the model builder from the layer's spec.
+    The add of a sublayer's normed output and the input norm of the sublayer after it are one kernel
+    (``add_post_norm``); the block leaves nothing pending."""
+
+    mixer_post_norm = None
+    ffn_post_norm = None
+
+    def parts(self):
+        return super().parts() + [p for p in (self.mixer_post_norm, self.ffn_post_norm) if p is not None]
+
+    def forward(self, residual, pending, ctx, cache, state):
+        rt = self.rt
+        T = ctx.T
+        ctx.block_hand = None
+        x = rt.workspace.get("block.normed", (rt.max_tokens, residual.shape[1]), rt.dtype)[:T]
+        self.mixer_norm.add_norm(residual, pending, x, rows=T)
+        op_mark(ctx, "add+norm", nbytes=PreNormBlock._norm_bytes(residual, pending, x))
+        a = self.mixer.forward(x, ctx, cache, state)
+        if self.ffn is None:
+            self.mixer_post_norm.add_post_norm(residual, a, None, None, rows=T)
+            op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, a, x))
+            return None
+        if not self.mixer_post_norm.add_post_norm(residual, a, self.ffn_norm, x, rows=T):
+            self.ffn_norm.add_norm(residual, None, x, rows=T)
+        op_mark(ctx, "post_norm+add+norm", nbytes=PreNormBlock._norm_bytes(residual, a, x))
+        f = self.ffn.forward(x, ctx)
+        self.ffn_post_norm.add_post_norm(residual, f, None, None, rows=T)
+        op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, f, x))
+        return None

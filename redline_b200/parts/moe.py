@@ -1,0 +1,167 @@
+"""Feed-forwards without a gate, W_down f(W_up h), alone ("act_mlp") or as a mixture of experts
+("routed_experts"): a router scores the experts per token in float32 (sigmoid or softmax), experts lie in
+equal groups of neighbours of which only the best ``group_keep`` (by the sum of their ``group_top`` best
+scores) can be chosen, the ``top`` best experts of those run for the token, weighted by their scores
+(as they are, or divided by their sum), and a shared expert of the same form may run for every token.
+The experts' products are grouped matrix products over (token, expert) pairs listed expert by expert on
+the device (csrc/moe.cu); nothing of the routing is read by the host.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import FeedForward, op_mark, register
+from .spec import TensorSpec
+
+
+@dataclass(frozen=True)
+class ActMLPParams:
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu_squared"     # a name of ops.kernels.ACTIVATIONS
+
+
+@register("ffn", "act_mlp")
+class ActMLP(FeedForward):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.act = kernels.ACTIVATIONS[self.params.activation]
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        p = self.params
+        return {"up": TensorSpec((p.intermediate_size, p.hidden_size)),
+                "down": TensorSpec((p.hidden_size, p.intermediate_size))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = tensors["up"], tensors["down"]
+
+    def nbytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
+
+    def run(self, x, ctx, name: str) -> torch.Tensor:
+        p, rt = self.params, self.rt
+        T = ctx.T
+        act = rt.workspace.get(name + ".act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
+        linear(x, self.w_up, act)
+        kernels.bias_act(act, None, self.act)
+        op_mark(ctx, "up+act", self.w_up, T)
+        out = rt.workspace.get(name + ".out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        linear(act, self.w_down, out)
+        op_mark(ctx, "down_proj", self.w_down, T)
+        return out
+
+    def forward(self, x, ctx) -> torch.Tensor:
+        return self.run(x, ctx, "ffn")
+
+
+@dataclass(frozen=True)
+class RoutedExpertsParams:
+    hidden_size: int
+    intermediate_size: int               # of one expert
+    num_experts: int
+    top: int
+    groups: int = 1
+    group_keep: int = 1
+    group_top: int = 2                   # a group is scored by the sum of its so many best experts
+    score: str = "sigmoid"               # or "softmax"
+    renormalize: bool = False            # divide the chosen weights by their sum
+    activation: str = "gelu"
+    shared_intermediate_size: int = 0    # 0: no shared expert
+    shared_activation: Optional[str] = None
+
+
+@register("ffn", "routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.params
+        if p.num_experts % p.groups != 0 or not 1 <= p.group_keep <= p.groups:
+            raise ValueError(f"{p.num_experts} experts do not form {p.groups} equal groups of which {p.group_keep} stay")
+        if not 1 <= p.top <= p.group_keep * (p.num_experts // p.groups):
+            raise ValueError(f"top {p.top} experts cannot be chosen among {p.group_keep} groups of "
+                             f"{p.num_experts // p.groups}")
+        if p.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"router score '{p.score}' is not supported (sigmoid, softmax)")
+        self.act = kernels.ACTIVATIONS[p.activation]
+        self.shared = None
+        if p.shared_intermediate_size > 0:
+            from .spec import PartSpec
+            self.shared = ActMLP(PartSpec("act_mlp", ActMLPParams(p.hidden_size, p.shared_intermediate_size,
+                                                                  p.shared_activation or p.activation)), rt)
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        p = self.params
+        t = {"router": TensorSpec((p.num_experts, p.hidden_size))}
+        for e in range(p.num_experts):
+            t[f"up{e}"] = TensorSpec((p.intermediate_size, p.hidden_size))
+            t[f"down{e}"] = TensorSpec((p.hidden_size, p.intermediate_size))
+        if self.shared is not None:
+            t["shared_up"] = TensorSpec((p.shared_intermediate_size, p.hidden_size))
+            t["shared_down"] = TensorSpec((p.hidden_size, p.shared_intermediate_size))
+        return t
+
+    def fused(self) -> Dict[str, list]:
+        n = self.params.num_experts
+        return {"up_all": [f"up{e}" for e in range(n)], "down_all": [f"down{e}" for e in range(n)]}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        p = self.params
+
+        def stacked(fused_name: str, stem: str) -> torch.Tensor:
+            if fused_name in tensors:
+                return tensors[fused_name]
+            ws = [tensors[f"{stem}{e}"] for e in range(p.num_experts)]
+            dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+            return torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
+
+        self.w_up = stacked("up_all", "up")            # [experts * ff, hidden]
+        self.w_down = stacked("down_all", "down")      # [experts * hidden, ff]
+        self.w_router = tensors["router"]
+        if self.shared is not None:
+            self.shared.load({"up": tensors["shared_up"], "down": tensors["shared_down"]})
+
+    def nbytes(self) -> int:
+        n = sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down, self.w_router))
+        return n + (self.shared.nbytes() if self.shared is not None else 0)
+
+    def forward(self, x, ctx) -> torch.Tensor:
+        p, rt = self.params, self.rt
+        T = ctx.T
+        ws = rt.workspace
+        pairs = T * p.top
+        max_pairs = rt.max_tokens * p.top
+        max_tiles = kernels.moe_max_tiles(pairs, p.num_experts)
+        cap_tiles = kernels.moe_max_tiles(max_pairs, p.num_experts)
+        choice = ws.get("moe.choice", (max_pairs,), torch.int32)
+        weight = ws.get("moe.weight", (max_pairs,), torch.float32)
+        order = ws.get("moe.order", (max_pairs,), torch.int32)
+        tile_expert = ws.get("moe.tile_expert", (cap_tiles,), torch.int32)
+        tile_begin = ws.get("moe.tile_begin", (cap_tiles,), torch.int32)
+        tile_rows = ws.get("moe.tile_rows", (cap_tiles,), torch.int32)
+        meta = ws.get("moe.meta", (4,), torch.int32)
+        kernels.moe_route(x, self.w_router, choice, weight, T, p.groups, p.group_keep, p.group_top, p.top,
+                          softmax=p.score == "softmax", renorm=p.renormalize)
+        kernels.moe_group(choice, pairs, p.num_experts, order, tile_expert, tile_begin, tile_rows, meta)
+        op_mark(ctx, "route", self.w_router, T)
+        if x.dtype != self.w_up.dtype:
+            raise kernels.KernelError("routed_experts: expert weights must have the activation type")
+        act = ws.get("moe.act", (max_pairs, p.intermediate_size), rt.dtype)[:pairs]
+        y = ws.get("moe.y", (max_pairs, p.hidden_size), rt.dtype)[:pairs]
+        lists = (order, tile_expert, tile_begin, tile_rows, meta, max_tiles)
+        kernels.moe_gemm(x, p.top, self.w_up, act, *lists, act=self.act)
+        kernels.moe_gemm(act, 1, self.w_down, y, *lists)
+        elem = x.element_size()
+        op_mark(ctx, "experts", nbytes=float(min(pairs, p.num_experts) * 2 * p.intermediate_size * p.hidden_size * elem
+                                             + pairs * (2 * p.intermediate_size + 2 * p.hidden_size) * elem),
+                flops=4.0 * pairs * p.intermediate_size * p.hidden_size)
+        shared = self.shared.run(x, ctx, "moe.shared") if self.shared is not None else None
+        out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        kernels.moe_combine(y, weight, shared, out, T, p.top)
+        op_mark(ctx, "combine", nbytes=float((pairs + 2 * T) * p.hidden_size * elem))
+        return out

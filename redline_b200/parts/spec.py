@@ -35,6 +35,9 @@ class LayerSpec:
     mixer: PartSpec
     ffn_norm: Optional[PartSpec] = None
     ffn: Optional[PartSpec] = None
+    # for arrangements that also norm what a sublayer puts out, before it is added to the stream
+    mixer_post_norm: Optional[PartSpec] = None
+    ffn_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -96,7 +99,8 @@ class CacheTensor:
 class CacheSpec:
     """What a mixer needs cached for each token it has seen.
 
-    kind     "full": every token stays; "window": only the last ``window`` tokens
+    kind     "full": every token stays; "window": only the last ``window`` tokens (and the first
+             ``keep_first`` ones, if the mixer's mask keeps them visible)
     tensors  the tensors kept per token, each with a shape of its own (keys and values of the same
              shape for ordinary attention; one latent vector, or keys and values of different widths,
              for other mixers)
@@ -106,6 +110,7 @@ class CacheSpec:
     kind: str
     tensors: Tuple[CacheTensor, ...]
     window: int = 0
+    keep_first: int = 0      # in a window group: the first so many tokens of a sequence stay (their pages are kept)
 
     @staticmethod
     def keys_values(kind: str, heads: int, head_dim: int, window: int = 0) -> "CacheSpec":
@@ -116,7 +121,7 @@ class CacheSpec:
         return sum(t.elements() for t in self.tensors)
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.tensors, self.window)
+        return (self.kind, self.tensors, self.window, self.keep_first)
 
 
 @dataclass(frozen=True)
