@@ -1,0 +1,223 @@
+"""The kernels added for Kapitar, one by one, against float64 restatements (tests/plain_kapitar.py and
+this file): norms on both sides of a sublayer, bias + activation, the gated unit norm, the linear-attention
+recurrence (serial and cut into chunks, from a given state), the router (groups, kept groups, top
+experts), the experts' grouped products with the routing given, their weighted sum."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kapitar as K
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def rel(a, b):
+    return float((a.double().cpu() - b.double().cpu()).abs().max() / (b.double().abs().max() + 1e-30))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("hidden", [96, 320, 2500])
+def test_norms_around_a_sublayer(dtype, tol, hidden):
+    from redline_b200.ops import kernels
+    g = torch.Generator().manual_seed(hidden)
+    T = 19
+    res = (torch.randn(T, hidden, generator=g) * 3 + 1.5).to(DEV)          # a mean well away from zero
+    delta = (torch.randn(T, hidden, generator=g) * 2 - 0.7).to(dtype).to(DEV)
+    wb = (1 + 0.2 * torch.randn(hidden, generator=g)).to(dtype).to(DEV)
+    wn = (1 + 0.2 * torch.randn(hidden, generator=g)).to(dtype).to(DEV)
+    eps = 1e-5
+    for kind, norm in ((kernels.NORM_LAYER, K.layer_norm),
+                       (kernels.NORM_RMS, lambda x, w, e: K.unit_rms(x, e) * w)):
+        r = res.clone()
+        out = torch.empty(T, hidden, dtype=dtype, device=DEV)
+        kernels.sandwich_norm(r, delta, wb, wn, out, eps, kind)
+        want_r = res.double() + norm(delta.double(), wb.double(), eps)
+        assert rel(r, want_r) < 2e-6
+        assert rel(out, norm(want_r, wn.double(), eps)) < tol
+        # a plain add, then the norm; and rows picked by index without an add
+        r = res.clone()
+        kernels.sandwich_norm(r, delta, None, wn, out, eps, kind)
+        assert rel(r, res.double() + delta.double()) < 1e-6
+        idx = torch.tensor([5, 0, 5, 18], dtype=torch.int32, device=DEV)
+        picked = torch.empty(4, hidden, dtype=dtype, device=DEV)
+        r = res.clone()
+        kernels.sandwich_norm(r, None, None, wn, picked, eps, kind, rows_idx=idx)
+        assert torch.equal(r, res)
+        assert rel(picked, norm(res.double()[idx.long()], wn.double(), eps)) < tol
+        # only the normed add
+        r = res.clone()
+        kernels.sandwich_norm(r, delta, wb, None, None, eps, kind)
+        assert rel(r, want_r) < 2e-6
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-2)])
+def test_bias_activation_and_gated_norm(dtype, tol):
+    from redline_b200.ops import kernels
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(7, 200, generator=g) * 2).to(dtype).to(DEV)
+    b = torch.randn(120, generator=g).to(DEV)
+    for name, f in (("relu_squared", lambda z: torch.relu(z) ** 2), ("gelu", K.gelu_erf), ("silu", K.silu),
+                    ("gelu_tanh", lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))))):
+        y = x.clone()
+        kernels.bias_act(y, b, kernels.ACTIVATIONS[name], cols=120)
+        z = (x[:, :120].double() + b.double())
+        if dtype == torch.bfloat16:
+            z = z.to(dtype).double()
+        assert rel(y[:, :120], f(z)) < tol
+        assert torch.equal(y[:, 120:], x[:, 120:])
+    o = (torch.randn(9, 72, generator=g) * 5).to(DEV)
+    buf = torch.randn(9, 200, generator=g).to(dtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(72, generator=g)).to(dtype).to(DEV)
+    out = torch.empty(9, 72, dtype=dtype, device=DEV)
+    kernels.gated_rmsnorm(o, buf[:, 100:172], w, out, 1e-6)
+    want = K.unit_rms(o.double(), 1e-6) * w.double() * torch.sigmoid(buf[:, 100:172].double())
+    assert rel(out, want) < tol
+
+
+def recurrence(q, k, v, decay, S):
+    """q, k [T, H, D], v [T, H, DV], S [H, D, DV] float64 -> (o [T, H, DV], final S)."""
+    S = S.clone()
+    o = torch.zeros(q.shape[0], q.shape[1], v.shape[2], dtype=torch.float64)
+    for t in range(q.shape[0]):
+        for h in range(q.shape[1]):
+            S[h] = decay[h] * S[h] + torch.outer(k[t, h], v[t, h])
+            o[t, h] = S[h].T @ q[t, h]
+    return o, S
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,D,DV", [(3, 16, 24), (1, 40, 130), (2, 64, 64)])
+def test_linear_attention_from_a_state_serial_and_in_chunks(dtype, H, D, DV):
+    """Three sequences of unequal length in one launch (one of a single token), each from its own
+    non-zero state in its own slot; long ones cut into chunks, with a last chunk of another length."""
+    from redline_b200.ops import kernels
+    g = torch.Generator().manual_seed(D)
+    lens = [333, 1, 70]
+    slots = [4, 0, 2]
+    decay = [0.999, 0.6, 0.9][:H]
+    T = sum(lens)
+    width = 2 * H * D + H * DV + 5
+    proj = (torch.randn(T, width, generator=g) * 0.5).to(dtype)
+    state0 = torch.randn(6, H, D, DV, generator=g)
+    seq_of = torch.tensor(sum(([i] * n for i, n in enumerate(lens)), []), dtype=torch.int32, device=DEV)
+    slot_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    dec = torch.tensor(decay, dtype=torch.float32, device=DEV)
+    want_o, want_S = [], {}
+    at = 0
+    for n, s in zip(lens, slots):
+        p = proj[at:at + n].double()
+        o, S = recurrence(p[:, :H * D].view(n, H, D), p[:, H * D:2 * H * D].view(n, H, D),
+                          p[:, 2 * H * D:2 * H * D + H * DV].view(n, H, DV), decay, state0[s].double())
+        want_o.append(o.reshape(n, H * DV))
+        want_S[s] = S
+        at += n
+    want_o = torch.cat(want_o)
+    for chunked in (False, True):
+        state = state0.clone().to(DEV)
+        out = torch.zeros(T, H * DV, device=DEV)
+        chunk, max_chunks = (64, (max(lens) + 63) // 64) if chunked else (0, 1)
+        scratch = torch.full((3 * max_chunks * H * D * DV,), float("nan"), device=DEV) if chunked else None
+        kernels.linear_attention(proj.to(DEV), 0, H * D, 2 * H * D, seq_of, slot_t, dec, state, out, T, 3, H, D, DV,
+                                 scratch, chunk, max_chunks)
+        assert rel(out, want_o) < (2e-5 if dtype == torch.float32 else 2e-5), chunked
+        for s in range(6):
+            if s in want_S:
+                assert rel(state[s], want_S[s]) < 2e-5
+            else:
+                assert torch.equal(state[s].cpu(), state0[s])          # other requests' slots are not touched
+    assert kernels.linear_attention_chunks(100) == (0, 1)
+    c, m = kernels.linear_attention_chunks(5000)
+    assert c * m >= 5000 and m <= kernels.LINEAR_ATTN_MAX_CHUNKS
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,groups,keep,top", [(8, 4, 2, 3), (16, 2, 1, 4), (6, 1, 1, 1), (12, 3, 3, 5), (64, 8, 3, 6)])
+def test_router(dtype, E, groups, keep, top):
+    from redline_b200.ops import kernels
+    g = torch.Generator().manual_seed(E + top)
+    T, W = 200, 72
+    x = torch.randn(T, W, generator=g).to(dtype)
+    wr = (torch.randn(E, W, generator=g) * 0.3).to(dtype)
+    r = {"groups": {"count": groups, "keep": keep}, "top": top}
+    choice, weight = K.route(x.double(), wr.double(), r)
+    got_c = torch.zeros(T, top, dtype=torch.int32, device=DEV)
+    got_w = torch.zeros(T, top, dtype=torch.float32, device=DEV)
+    kernels.moe_route(x.to(DEV), wr.to(DEV), got_c, got_w, T, groups, keep, 2, top)
+    # tokens whose choice hangs on a difference below the float32 noise of the scores are left out
+    s = torch.sigmoid(x.double() @ wr.double().T)
+    per = E // groups
+    gscore = s.view(T, groups, per).topk(min(2, per), dim=-1).values.sum(-1).sort(dim=-1, descending=True).values
+    clear = torch.ones(T, dtype=torch.bool)
+    if keep < groups:
+        clear &= (gscore[:, keep - 1] - gscore[:, keep]) > 1e-5
+    allowed = torch.zeros(T, E, dtype=torch.bool)
+    allowed.scatter_(1, choice, True)
+    ranked = torch.where(allowed, torch.full_like(s, 2.0), s)
+    kept_groups = torch.zeros(T, groups, dtype=torch.bool)
+    kept_groups.scatter_(1, choice // per, True)
+    runner_up = torch.where(kept_groups.repeat_interleave(per, dim=1) & ~allowed, s, torch.full_like(s, -1.0)).max(-1).values
+    clear &= (weight.min(-1).values - runner_up) > 1e-5
+    sorted_w = weight.sort(dim=-1, descending=True).values
+    if top > 1:
+        clear &= (sorted_w[:, :-1] - sorted_w[:, 1:]).min(-1).values > 1e-5
+    assert clear.float().mean() > 0.9
+    assert torch.equal(got_c.cpu().long()[clear], choice[clear])
+    assert rel(got_w.cpu()[clear], weight[clear]) < 1e-5
+    del ranked
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("T,E,top,W,ff", [(70, 8, 3, 96, 40), (5, 16, 4, 64, 24), (300, 4, 2, 72, 100), (1, 6, 1, 40, 8)])
+def test_experts_with_the_routing_given(dtype, tol, T, E, top, W, ff):
+    """Pairs listed expert by expert in tiles, both grouped products and the weighted sum, against the
+    plain expert applied pair by pair.  Some experts get no token, one gets more than a tile."""
+    from redline_b200.ops import kernels
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, W, generator=g).to(dtype)
+    up = (torch.randn(E, ff, W, generator=g) / math.sqrt(W)).to(dtype)
+    down = (torch.randn(E, W, ff, generator=g) / math.sqrt(ff)).to(dtype)
+    shared = torch.randn(T, W, generator=g).to(dtype)
+    choice = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(T)]).to(torch.int32)   # expert E-1: none
+    if T > 40:
+        choice[:40, 0] = 0                                                                               # expert 0: > 32 pairs
+        for t in range(40):
+            if (choice[t, 1:] == 0).any():
+                choice[t, 1:][choice[t, 1:] == 0] = E - 1
+    weight = torch.rand(T, top, generator=g)
+    w = {}
+    for e in range(E):
+        w[f"e{e}.up"], w[f"e{e}.down"] = up[e].float(), down[e].float()
+    K.STORE_DTYPE = None if dtype == torch.float32 else dtype
+    try:
+        want = torch.zeros(T, W, dtype=torch.float64)
+        for t in range(T):
+            for k in range(top):
+                y = K.expert(x[t:t + 1].double(), w, f"e{int(choice[t, k])}.")[0]
+                want[t] += float(weight[t, k]) * K.stored(y)
+        want += shared.double()
+    finally:
+        K.STORE_DTYPE = None
+    pairs = T * top
+    tiles = kernels.moe_max_tiles(pairs, E)
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=DEV)      # noqa: E731
+    order, te, tb, trw, meta = i32(pairs), i32(tiles), i32(tiles), i32(tiles), i32(4)
+    kernels.moe_group(choice.to(DEV).reshape(-1), pairs, E, order, te, tb, trw, meta)
+    n_tiles = int(meta[0])
+    counts = torch.bincount(choice.reshape(-1).long(), minlength=E)
+    assert n_tiles == int(((counts + 31) // 32).sum())
+    assert sorted(order.cpu().tolist()) == list(range(pairs))
+    listed = choice.reshape(-1)[order.cpu().long()]
+    assert torch.equal(listed, listed.sort().values)                    # expert by expert
+    act = torch.full((pairs, ff), float("nan"), dtype=dtype, device=DEV)
+    y = torch.full((pairs, W), float("nan"), dtype=dtype, device=DEV)
+    xd = x.to(DEV)
+    kernels.moe_gemm(xd, top, up.to(DEV).reshape(E * ff, W), act, order, te, tb, trw, meta, tiles, act=kernels.ACT_GELU_ERF)
+    kernels.moe_gemm(act, 1, down.to(DEV).reshape(E * W, ff), y, order, te, tb, trw, meta, tiles)
+    out = torch.empty(T, W, dtype=dtype, device=DEV)
+    kernels.moe_combine(y, weight.to(DEV), shared.to(DEV), out, T, top)
+    assert rel(out, want) < tol
