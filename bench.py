@@ -502,6 +502,11 @@ def main() -> int:
     ap.add_argument("--profile-batch", type=int, default=BATCH)
     ap.add_argument("--profile-prompt", type=int, default=0, help="with --profile-step: prompt length (default: context - 96)")
     ap.add_argument("--profile-eager", action="store_true", help="with --profile-step: no CUDA graph")
+    ap.add_argument("--compare-design", default="", choices=["", "kapitar"],
+                    help="instead of the headline run: prefill and decode throughput of this architecture beside "
+                         "Llama at equal layer sizes, with the per-op roofline fractions of both")
+    ap.add_argument("--compare-sizes", default="s,m", help="with --compare-design: which of its sizes (s, m)")
+    ap.add_argument("--compare-no-ops", action="store_true", help="with --compare-design: no per-op tables")
     args = ap.parse_args()
     if args.gpus != 1:
         print("redline_b200 is a single-GPU engine: bench.py runs at --gpus 1 only")
@@ -512,6 +517,17 @@ def main() -> int:
         return profile_prefill(args)
     args.warmup = max(args.warmup, 3)
     args.steps = max(1, min(args.steps, 1000))
+    if args.compare_design:
+        from redline_b200.apps import design_bench
+        pk = peaks()
+        sampler = ClockSampler()
+        sampler.start()
+        res = design_bench.compare(args.compare_design, [x for x in args.compare_sizes.split(",") if x], min(args.steps, 64),
+                                   args.warmup, BATCH, pk["hbm_gbs"], pk["bf16_tflops"], with_ops=not args.compare_no_ops)
+        sampler.stop()
+        res.update(peaks=pk.get("source", ""), hbm_gbs=pk["hbm_gbs"], bf16_tflops=pk["bf16_tflops"], clocks=sampler.summary())
+        print(json.dumps(res))
+        return 0
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(res))
     return 0

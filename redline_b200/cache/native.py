@@ -80,6 +80,7 @@ def lib() -> ctypes.CDLL:
             "rl_hc_build": (c_int, [c_void_p, c_void_p, POINTER(RlLayout), i32p, i32p, c_int, c_int, c_int,
                                     c_void_p, c_void_p, c_void_p, c_int, c_int, i32p]),
             "rl_hc_pad": (None, [c_void_p, POINTER(RlLayout), c_int, c_int]),
+            "rl_hc_pad_state": (None, [c_void_p, POINTER(RlLayout), c_int, c_int, c_int]),
             "rl_sched_plan": (c_int, [c_void_p, POINTER(RlSchedCfg), c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p]),
         }

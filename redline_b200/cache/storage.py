@@ -48,13 +48,21 @@ class CacheStorage:
 
 
 class StateStorage:
-    """Pools of fixed-size per-request state, one per layer call that keeps state."""
+    """Pools of fixed-size per-request state, one per layer call that keeps state.  A pool has one slot more
+    than the manager hands out: index ``num_slots`` belongs to the padding rows of fixed-shape batches."""
 
     def __init__(self, specs: Dict[int, StateSpec], num_slots: int, device: torch.device):
         self.pools: Dict[int, torch.Tensor] = {
-            call: torch.zeros((num_slots,) + tuple(s.shape), dtype=getattr(torch, s.dtype), device=device)
+            call: torch.zeros((num_slots + 1,) + tuple(s.shape), dtype=getattr(torch, s.dtype), device=device)
             for call, s in specs.items()
         }
+
+    def snapshot(self) -> Dict[int, torch.Tensor]:
+        return {call: p.clone() for call, p in self.pools.items()}
+
+    def restore(self, saved: Dict[int, torch.Tensor]) -> None:
+        for call, p in self.pools.items():
+            p.copy_(saved[call])
 
     def of_call(self, call: int) -> Optional[torch.Tensor]:
         return self.pools.get(call)

@@ -17,8 +17,11 @@
 // Scores, softmax, the combination of the maps and the norm are float32 for both element types.
 // Single tokens: one CTA per (128-key partition, kv head, item) over absolute partitions, so a row's
 // sums do not depend on what else is in the launch; a second kernel merges the partitions of a head's
-// maps, combines them and norms.  Prompt portions: one CTA per (32 query rows, head), both maps in
-// turn over the visible key tiles, combination and norm in the epilogue.
+// maps, combines them and norms.  Prompt portions: both maps in turn over the visible key tiles,
+// combination and norm in the epilogue; in bfloat16 with sizes that are multiples of 16 on the tensor
+// cores (one CTA per 64 query rows and head), else on CUDA cores (one CTA per 32 query rows and head).
+#include <cstring>
+
 #include "common.cuh"
 
 #if !defined(RL_QK_DIM) || !defined(RL_V_DIM) || !defined(RL_MAPS)
@@ -43,22 +46,16 @@ struct MaskArgs {
 __device__ __forceinline__ bool key_visible(int j, int i, const MaskArgs& mk) {
   return j <= i && (mk.window <= 0 || i - j < mk.window || j < mk.keep_first);
 }
+// Whether key j is behind the window of position i and of every later one, and not kept: its page may have
+// been given back, so it is not read at all (a masked weight of zero times a stray NaN would be NaN).
+__device__ __forceinline__ bool dead_key(int j, int i, const MaskArgs& mk) {
+  return mk.window > 0 && j >= mk.keep_first && j <= i - mk.window;
+}
 // Whether keys [lo, hi) hold one that position i sees.
 __device__ __forceinline__ bool range_visible(int lo, int hi, int i, const MaskArgs& mk) {
   if (lo > i || lo >= hi) return false;
   if (mk.window <= 0) return true;
   return lo < mk.keep_first || hi > i - mk.window + 1;
-}
-
-template <typename T>
-__device__ __forceinline__ void load_row(const T* __restrict__ p, int n, float* out) {
-  // n elements from p (16-byte aligned when n is a multiple of the vector width)
-  constexpr int VEC = Vec16<T>::N;
-  if (n % VEC == 0) {
-    for (int c = 0; c < n; c += VEC) load16(p + c, out + c);
-  } else {
-    for (int c = 0; c < n; ++c) out[c] = to_float(p[c]);
-  }
 }
 
 template <typename T>
@@ -368,7 +365,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
         const int key = i / kD, d = i - key * kD;
         const int j = k0 + key;
         float v = 0.f;
-        if (j < k_end) {
+        if (j < k_end && !dead_key(j, pos0, a.mask)) {
           const size_t page = bt[j / a.page_size];
           v = to_float(a.kcache[((page * (a.kv_heads * kM) + kvh * kM + m) * a.page_size + j % a.page_size) * kD + d]);
         }
@@ -378,7 +375,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
         const int key = i / kDV, d = i - key * kDV;
         const int j = k0 + key;
         float v = 0.f;
-        if (j < k_end) {
+        if (j < k_end && !dead_key(j, pos0, a.mask)) {
           const size_t page = bt[j / a.page_size];
           v = to_float(a.vcache[((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV + d]);
         }
@@ -448,6 +445,250 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
   }
 }
 
+// ------------------------------------------------------------------ prompt portions on the tensor cores
+// bfloat16, key and value sizes that are multiples of 16.  One CTA of four warps takes 64 query rows of a
+// tile for one head; a warp takes 16 of them.  Keys and values come in tiles of 64 from the paged cache
+// into shared memory (16-byte pieces, rows padded by 16 bytes so that fragment reads meet no bank twice).
+// S = Q K^T with mma.sync.m16n8k16 (Q fragments straight from global memory, once per map), scale, cap,
+// mask and online softmax in float32 in the accumulator layout; O += P V with V fragments from
+// ldmatrix.trans.  The weights P are not cut to 16 bits: P = P_hi + P_lo (two bfloat16 operands, two MMAs
+// into the same float32 accumulator), which keeps 16 bits of mantissa.  Both maps run in turn over the
+// visible tiles; the first map's result waits in shared memory; combination, unit norm and the bfloat16
+// store are the epilogue.
+#if (RL_QK_DIM % 16 == 0) && (RL_V_DIM % 16 == 0)
+#define RL_MAPS_HAVE_MMA 1
+constexpr int kTQ = 64, kTK = 64;
+constexpr int kLDK = kD + 8, kLDV = kDV + 8;      // shared-memory row lengths in elements
+
+__device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// tanh with an ABSOLUTE error of a few 1e-7 (what a score needs: it goes into an exponential), from one
+// fast exponential and one fast division; the hardware's tanh.approx is good to 2^-11 only.
+__device__ __forceinline__ float tanh_fast(float x) {
+  return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);
+}
+
+__global__ void __launch_bounds__(128)
+maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [64][D + 8]
+  bf16* Vs = Ks + kTK * kLDK;                                    // [64][DV + 8]
+  float* O0 = reinterpret_cast<float*>(Vs + kTK * kLDV);         // [64][DV], the first map's result (two maps)
+
+  const int halves = a.tile_quarters;                            // 64-row parts of a tile of the launch
+  const int tile = blockIdx.x / halves, part = blockIdx.x % halves, head = blockIdx.y;
+  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile] + part * kTQ;
+  const int rows = min(a.tile_rows[tile] - part * kTQ, kTQ);
+  if (rows <= 0) return;
+  const int kvh = head / (a.heads / a.kv_heads);
+  const int pos0 = a.positions[tok0];
+  const int k_end = pos0 + rows;
+  const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int r0 = warp * 16 + gid, r1 = r0 + 8;                   // this thread's two rows within the CTA's 64
+  const int p0 = pos0 + r0, p1 = pos0 + r1;
+  const bool ok0 = r0 < rows, ok1 = r1 < rows;
+  const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+
+  float o[kDV / 8][4];
+  for (int m = 0; m < kM; ++m) {
+    // ---- Q fragments of this map
+    uint32_t qf[kD / 16][4];
+    {
+      const bf16* q0 = a.q + static_cast<size_t>(tok0 + r0) * a.q_stride + (head * kM + m) * kD + tig * 2;
+      const bf16* q1 = a.q + static_cast<size_t>(tok0 + r1) * a.q_stride + (head * kM + m) * kD + tig * 2;
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks) {
+        qf[ks][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16) : 0u;
+        qf[ks][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16) : 0u;
+        qf[ks][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8) : 0u;
+        qf[ks][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8) : 0u;
+      }
+    }
+#pragma unroll
+    for (int nd = 0; nd < kDV / 8; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
+    float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    for (int k0 = 0; k0 < k_end; k0 += kTK) {
+      const int t_hi = min(k0 + kTK, k_end);
+      if (a.mask.window > 0 && k0 >= a.mask.keep_first && t_hi <= pos0 - a.mask.window + 1) continue;
+      __syncthreads();                       // the tile before has been read by every warp
+      for (int i = threadIdx.x; i < kTK * (kD / 8); i += 128) {
+        const int key = i / (kD / 8), c = i - key * (kD / 8);
+        const int j = k0 + key;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j < k_end && !dead_key(j, pos0, a.mask)) {
+          const size_t page = bt[j / a.page_size];
+          v = *reinterpret_cast<const uint4*>(a.kcache + ((page * (a.kv_heads * kM) + kvh * kM + m) * a.page_size +
+                                                           j % a.page_size) * kD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(Ks + key * kLDK + c * 8) = v;
+      }
+      for (int i = threadIdx.x; i < kTK * (kDV / 8); i += 128) {
+        const int key = i / (kDV / 8), c = i - key * (kDV / 8);
+        const int j = k0 + key;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j < k_end && !dead_key(j, pos0, a.mask)) {
+          const size_t page = bt[j / a.page_size];
+          v = *reinterpret_cast<const uint4*>(a.vcache + ((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV +
+                                              c * 8);
+        }
+        *reinterpret_cast<uint4*>(Vs + key * kLDV + c * 8) = v;
+      }
+      __syncthreads();
+      // ---- S = Q K^T: 16 rows x 64 keys per warp
+      float s[kTK / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < kTK / 8; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        const bf16* kr = Ks + (nt * 8 + gid) * kLDK + tig * 2;
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks)
+          mma_16816(s[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kr + ks * 16),
+                    *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8));
+      }
+      // ---- scale, cap, mask; the rows' maxima
+      float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < kTK / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = k0 + nt * 8 + tig * 2 + (e & 1);
+          float v = s[nt][e] * a.scale;
+          if (a.softcap > 0.f) v = a.softcap * tanh_fast(v * inv_cap);
+          const bool vis = (e < 2) ? (ok0 && key_visible(j, p0, a.mask)) : (ok1 && key_visible(j, p1, a.mask));
+          v = vis ? v : -INFINITY;
+          s[nt][e] = v;
+          if (e < 2) t0 = fmaxf(t0, v);
+          else t1 = fmaxf(t1, v);
+        }
+      }
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+      const float n0 = fmaxf(mx0, t0), n1 = fmaxf(mx1, t1);
+      const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;
+      const float al0 = mx0 == -INFINITY ? 0.f : __expf(mx0 - u0), al1 = mx1 == -INFINITY ? 0.f : __expf(mx1 - u1);
+      mx0 = n0;
+      mx1 = n1;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < kTK / 8; ++nt) {
+        s[nt][0] = __expf(s[nt][0] - u0);
+        s[nt][1] = __expf(s[nt][1] - u0);
+        s[nt][2] = __expf(s[nt][2] - u1);
+        s[nt][3] = __expf(s[nt][3] - u1);
+        sum0 += s[nt][0] + s[nt][1];
+        sum1 += s[nt][2] + s[nt][3];
+      }
+      l0 = l0 * al0 + sum0;                  // (a quad's four partial sums are added at the end)
+      l1 = l1 * al1 + sum1;
+#pragma unroll
+      for (int nd = 0; nd < kDV / 8; ++nd) {
+        o[nd][0] *= al0;
+        o[nd][1] *= al0;
+        o[nd][2] *= al1;
+        o[nd][3] *= al1;
+      }
+      // ---- O += P V, P as a high and a low bfloat16 part
+#pragma unroll
+      for (int kk = 0; kk < kTK / 16; ++kk) {
+        uint32_t ph[4], pl[4];
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const float x = s[2 * kk + (f >> 1)][(f & 1) * 2], y = s[2 * kk + (f >> 1)][(f & 1) * 2 + 1];
+          const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+          ph[f] = *reinterpret_cast<const uint32_t*>(&h);
+          pl[f] = pack_bf16(x - __low2float(h), y - __high2float(h));
+        }
+        const bf16* vrow = Vs + (kk * 16 + (lane & 15)) * kLDV + (lane >> 4) * 8;
+#pragma unroll
+        for (int nd = 0; nd < kDV / 8; nd += 2) {
+          uint32_t b0, b1, b2, b3;
+          const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(vrow + nd * 8));
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+          mma_16816(o[nd], ph, b0, b1);
+          mma_16816(o[nd], pl, b0, b1);
+          mma_16816(o[nd + 1], ph, b2, b3);
+          mma_16816(o[nd + 1], pl, b2, b3);
+        }
+      }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (kM == 2 && m == 0) {
+      // (every thread reads back exactly what it wrote: no barrier is needed for O0)
+#pragma unroll
+      for (int nd = 0; nd < kDV / 8; ++nd) {
+        float* w0 = O0 + r0 * kDV + nd * 8 + tig * 2;
+        float* w1 = O0 + r1 * kDV + nd * 8 + tig * 2;
+        w0[0] = o[nd][0] * i0;
+        w0[1] = o[nd][1] * i0;
+        w1[0] = o[nd][2] * i1;
+        w1[1] = o[nd][3] * i1;
+      }
+    } else if (kM == 2) {
+#pragma unroll
+      for (int nd = 0; nd < kDV / 8; ++nd) {
+        const float* w0 = O0 + r0 * kDV + nd * 8 + tig * 2;
+        const float* w1 = O0 + r1 * kDV + nd * 8 + tig * 2;
+        o[nd][0] = w0[0] - a.lambda * o[nd][0] * i0;
+        o[nd][1] = w0[1] - a.lambda * o[nd][1] * i0;
+        o[nd][2] = w1[0] - a.lambda * o[nd][2] * i1;
+        o[nd][3] = w1[1] - a.lambda * o[nd][3] * i1;
+      }
+    } else {
+#pragma unroll
+      for (int nd = 0; nd < kDV / 8; ++nd) {
+        o[nd][0] *= i0;
+        o[nd][1] *= i0;
+        o[nd][2] *= i1;
+        o[nd][3] *= i1;
+      }
+    }
+  }
+  float g0 = 1.f, g1 = 1.f;
+  if (a.unit_norm) {
+    float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+    for (int nd = 0; nd < kDV / 8; ++nd) {
+      q0 += o[nd][0] * o[nd][0] + o[nd][1] * o[nd][1];
+      q1 += o[nd][2] * o[nd][2] + o[nd][3] * o[nd][3];
+    }
+    q0 += __shfl_xor_sync(0xffffffffu, q0, 1);
+    q0 += __shfl_xor_sync(0xffffffffu, q0, 2);
+    q1 += __shfl_xor_sync(0xffffffffu, q1, 1);
+    q1 += __shfl_xor_sync(0xffffffffu, q1, 2);
+    g0 = rsqrtf(q0 / static_cast<float>(kDV) + a.eps) * a.post_scale;
+    g1 = rsqrtf(q1 / static_cast<float>(kDV) + a.eps) * a.post_scale;
+  }
+#pragma unroll
+  for (int nd = 0; nd < kDV / 8; ++nd) {
+    if (ok0)
+      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok0 + r0) * a.out_stride + head * kDV + nd * 8 + tig * 2) =
+          __floats2bfloat162_rn(o[nd][0] * g0, o[nd][1] * g0);
+    if (ok1)
+      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok0 + r1) * a.out_stride + head * kDV + nd * 8 + tig * 2) =
+          __floats2bfloat162_rn(o[nd][2] * g1, o[nd][3] * g1);
+  }
+}
+#endif  // sizes that are multiples of 16
+
+
 template <typename T>
 int launch_maps_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt, int max_blocks,
                        const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out, int out_stride,
@@ -488,7 +729,7 @@ int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void*
                         const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
                         const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
                         int kv_heads, int page_size, int window, int keep_first, float scale, float softcap,
-                        float lambda, float post_scale, float eps, int unit_norm, cudaStream_t stream) {
+                        float lambda, float post_scale, float eps, int unit_norm, int impl, cudaStream_t stream) {
   MapsPrefillArgs<T> a;
   a.q = static_cast<const T*>(q);
   a.q_stride = q_stride;
@@ -514,6 +755,25 @@ int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void*
   a.post_scale = post_scale;
   a.eps = eps;
   a.unit_norm = unit_norm;
+#ifdef RL_MAPS_HAVE_MMA
+  if (sizeof(T) == 2 && impl != 1 && q_stride % 2 == 0 && out_stride % 2 == 0 &&
+      reinterpret_cast<uintptr_t>(q) % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0 &&
+      reinterpret_cast<uintptr_t>(kc) % 16 == 0 && reinterpret_cast<uintptr_t>(vc) % 16 == 0) {
+    MapsPrefillArgs<bf16> b;
+    static_assert(sizeof(b) == sizeof(a), "one layout for both element types");
+    memcpy(&b, &a, sizeof(b));
+    b.tile_quarters = (tile_rows_max + kTQ - 1) / kTQ;
+    const size_t need = (kTK * kLDK + kTK * kLDV) * sizeof(bf16) + (kM == 2 ? kTQ * kDV * sizeof(float) : 0);
+    static bool mma_attr_set = false;
+    if (!mma_attr_set && need > 48 * 1024) {
+      cudaFuncSetAttribute(maps_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(need));
+      mma_attr_set = true;
+    }
+    return static_cast<int>(launch_kernel(maps_prefill_mma_kernel, dim3(tiles * b.tile_quarters, heads), dim3(128), need,
+                                          stream, b));
+  }
+#endif
+  if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);      // the tensor-core kernel was asked for
   const size_t smem = (kBQ * (kD + 1) + kBK * (kD + 1) + kBK * kDV + kBQ * (kBK + 1)) * sizeof(float);
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
@@ -551,15 +811,15 @@ int rl_maps_prefill(int dtype, const void* q, int q_stride, const void* kc, cons
                     int max_blocks, const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
                     const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
                     int kv_heads, int page_size, int window, int keep_first, float scale, float softcap, float lambda,
-                    float post_scale, float eps, int unit_norm, cudaStream_t stream) {
+                    float post_scale, float eps, int unit_norm, int impl, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (dtype == 0)
     return launch_maps_prefill<float>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
                                       out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
-                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, stream);
+                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, impl, stream);
   return launch_maps_prefill<bf16>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
                                    out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
-                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, stream);
+                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, impl, stream);
 }
 
 }  // extern "C"

@@ -461,6 +461,12 @@ void rl_hc_pad(int32_t* out, const RlLayout* lay, int from, int to) {
   }
 }
 
+// The padding rows' state slot: one that no request holds (the pools have one slot more than the
+// manager hands out), so that a state-keeping layer's padding rows disturb nobody.
+void rl_hc_pad_state(int32_t* out, const RlLayout* lay, int from, int to, int slot) {
+  for (int i = from; i < to; ++i) out[lay->state_slot + i] = slot;
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------ the scheduler's plan of one step

@@ -305,6 +305,8 @@ class BatchBuilder:
             if nd != S_real or R_real != S_real or T_real != S_real:
                 raise ValueError("only steps of single tokens that all want logits can be padded")
             self._lib.rl_hc_pad(h.ctypes.data, ctypes.byref(nl), S_real, pad_to)
+            # (the state pools have one slot beyond the manager's: the padding rows' own)
+            self._lib.rl_hc_pad_state(h.ctypes.data, ctypes.byref(nl), S_real, pad_to, self.cache.num_state_slots)
             nd = pad_to
             decode_parts = self.parts_capacity
         else:

@@ -98,6 +98,9 @@ class ModelRunner:
             else:
                 self._caches.append(self.storage.of_owner(call.cache_of, False))
         self._states = [self.states.of_call(i) for i in range(len(order))]
+        # state-keeping layers whose mixers cannot run inside a CUDA graph keep the whole model eager
+        self._eager_state = any(self.model.blocks[order[i].layer].mixer.state_in_graphs() is False
+                                for i in self.states.pools)
         self.model.nvtx_layers = cfg.nvtx_layers
         self.profiler = None                       # engine.profiler.OpProfiler while per-op profiling is on
         # one graph per padded size and per answer of the mixers to "which kernel for the single tokens", and
@@ -179,10 +182,10 @@ class ModelRunner:
 
     def _graph_bucket(self, segments: Sequence[Segment]) -> int:
         """The padded size at which this step is replayed as a CUDA graph, or 0 for an eager step.
-        A model whose mixers keep per-request state always steps eagerly: a graph's padding rows would
-        need a state slot of their own, and capturing runs the step more than once, which a state that
-        is updated in place does not survive."""
-        if self.states.pools:
+        A model with a state-keeping mixer that does not declare itself fit for graphs
+        (``Mixer.state_in_graphs``) always steps eagerly; for the others the padding rows use the state
+        pools' extra slot and ``_capture`` puts the states back after its extra run."""
+        if self._eager_state:
             return 0
         n = len(segments)
         for s in segments:
@@ -199,7 +202,7 @@ class ModelRunner:
         takes, which is what every step but the last of a long prompt is, and the whole step of a prompt of
         exactly that length), or None.  Such steps all launch the same kernels with the same arguments: where
         the portion starts, its pages and the wanted row are in the step's metadata on the device."""
-        if len(segments) != 1 or self.states.pools:
+        if len(segments) != 1 or self._eager_state:
             return None
         s = segments[0]
         n = len(s.tokens)
@@ -213,6 +216,7 @@ class ModelRunner:
         # (compiles kernels, sizes workspaces), is captured, and the first replay runs it
         # again: every kernel of a step gives the same result when repeated.
         fed = self.sampler.tokens.clone()       # the warm-up run overwrites what the step reads
+        states = self.states.snapshot()         # ... and advances the states, which the replay must start from
         self._forward(ctx, True, True)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
@@ -222,6 +226,7 @@ class ModelRunner:
         self._graph_kernels[key] = kernels.LAUNCHES - before
         self._graphs[key] = g
         self.sampler.tokens.copy_(fed)
+        self.states.restore(states)
         g.replay()
         return g
 

@@ -682,18 +682,19 @@ def maps_attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcac
                       tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,
                       tile_rows_max: int, heads: int, kv_heads: int, dim: int, vdim: int, maps: int, page_size: int,
                       window: int, keep_first: int, scale: float, softcap: float, lam: float, post_scale: float,
-                      eps: float, unit_norm: bool) -> None:
+                      eps: float, unit_norm: bool, impl: int = 0) -> None:
     """Tiles of up to ``tile_rows_max`` consecutive query tokens of one sequence; otherwise as
-    ``maps_attn_decode``."""
+    ``maps_attn_decode``.  impl 0: the best kernel that applies (bfloat16 with sizes that are multiples of
+    16: mma.sync tensor cores; else CUDA cores); 1: CUDA cores; 2: the tensor-core kernel or an error."""
     _need_cuda(q, kcache, vcache, out)
     f = _fn(_maps(dim, vdim, maps), "rl_maps_prefill",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
-             c_float, c_int, c_void_p])
+             c_float, c_int, c_int, c_void_p])
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
              _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions), _ptr(out), out.stride(0), tiles,
              tile_rows_max, heads, kv_heads, page_size, window, keep_first, float(scale), float(softcap), float(lam),
-             float(post_scale), float(eps), 1 if unit_norm else 0, _stream()), "maps_attn_prefill")
+             float(post_scale), float(eps), 1 if unit_norm else 0, impl, _stream()), "maps_attn_prefill")
 
 
 # ------------------------------------------------------- linear attention with a decaying state
@@ -837,9 +838,10 @@ def gather_logprob(logits: torch.Tensor, rows: int, target: torch.Tensor, out: t
            "gather_logprob")
 
 
-def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
-    """Compiles every kernel family (attention for the given head sizes) and removes built files of
-    these modules that belong to other versions of the sources."""
+def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2),), linear_dims=(64,), verbose: bool = True) -> None:
+    """Compiles every kernel family (attention for the given head sizes, attention with score maps for the
+    given (key size, value size, maps), linear attention for the given key sizes) and removes built files
+    of these modules that belong to other versions of the sources."""
     built = [
         build.compile_module("elementwise", "elementwise.cu", verbose=verbose),
         build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose),
@@ -853,4 +855,10 @@ def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
     ]
     for d in head_dims:
         built.append(build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose))
+    for d, v, m in maps_dims:
+        built.append(build.compile_module(f"attention_maps_d{d}_v{v}_m{m}", "attention_maps.cu",
+                                          {"RL_QK_DIM": d, "RL_V_DIM": v, "RL_MAPS": m}, verbose=verbose))
+    for d in linear_dims:
+        built.append(build.compile_module(f"linear_attention_d{d}", "linear_attention.cu", {"RL_LIN_DIM": d},
+                                          verbose=verbose))
     build.remove_other_versions(built)

@@ -218,6 +218,14 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def state_in_graphs(self) -> bool:
+        """Whether a mixer with a ``state_spec`` may run inside a CUDA graph: it finds sequences and slots
+        through the step's device metadata only (``ctx.seq_of_token``, ``ctx.state_slot``), never through
+        ``ctx.host``, and its launches depend on nothing but the step's shape.  The runner then replays
+        padded single-token steps as graphs (padding rows get a slot of their own) and restores the state
+        after the extra run that capturing needs.  Default: no, the model steps eagerly."""
+        return False
+
     def tiling(self) -> Optional[Tuple[int, int]]:
         """(query rows of a tile, keys of a partition) in which this mixer's kernels want the step's
         work lists cut (``ctx.tile_*`` for sequences that bring several tokens, ``ctx.decode_info`` /

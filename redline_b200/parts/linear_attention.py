@@ -54,6 +54,9 @@ class LinearAttention(Mixer):
         p = self.params
         return StateSpec((p.num_heads, p.dim, p.vdim), "float32")
 
+    def state_in_graphs(self) -> bool:
+        return True
+
     def tensors(self) -> Dict[str, TensorSpec]:
         p = self.params
         return {
@@ -90,7 +93,8 @@ class LinearAttention(Mixer):
         kernels.bias_act(proj, None, self.act, cols=2 * self.qk_size + self.v_size)
         op_mark(ctx, "qkvg_proj", self.w_in, T)
         o = ws.get("lin.o", (rt.max_tokens, self.v_size), torch.float32)[:T]
-        chunk, max_chunks = kernels.linear_attention_chunks(max(ctx.host.q_len))
+        # (how a step is cut depends on its shape alone: single-token steps and full portions replay as graphs)
+        chunk, max_chunks = kernels.linear_attention_chunks(1 if ctx.num_tiles == 0 else max(ctx.host.q_len))
         chunk_state = None
         if max_chunks > 1:
             chunk_state = ws.get("lin.chunks", (ctx.S * max_chunks * p.num_heads * p.dim * p.vdim,), torch.float32)

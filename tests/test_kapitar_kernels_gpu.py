@@ -221,3 +221,82 @@ def test_experts_with_the_routing_given(dtype, tol, T, E, top, W, ff):
     out = torch.empty(T, W, dtype=dtype, device=DEV)
     kernels.moe_combine(y, weight.to(DEV), shared.to(DEV), out, T, top)
     assert rel(out, want) < tol
+
+
+def attend(q, k, v, pos0, size, keep, scale, cap, lam, post, eps, unit):
+    """q [n, H, M, D] at positions pos0 .. pos0 + n - 1, k [L, G, M, D], v [L, G, DV], float64."""
+    n, H, M, D = q.shape
+    G = k.shape[1]
+    out = torch.zeros(n, H, v.shape[2], dtype=torch.float64)
+    for t in range(n):
+        i = pos0 + t
+        vis = torch.tensor([K.visible(i, j, size, keep) if size > 0 else j <= i for j in range(k.shape[0])])
+        for h in range(H):
+            g = h // (H // G)
+            maps = []
+            for m in range(M):
+                s = (k[:, g, m] @ q[t, h, m]) * scale
+                if cap > 0:
+                    s = cap * torch.tanh(s / cap)
+                s = s.masked_fill(~vis, -math.inf)
+                maps.append(torch.softmax(s, 0) @ v[:, g])
+            o = maps[0] if M == 1 else maps[0] - lam * maps[1]
+            out[t, h] = K.unit_rms(o, eps) * post if unit else o
+    return out.reshape(n, -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,M,D,DV,size,keep,cap", [
+    (4, 2, 2, 16, 32, 24, 3, 12.0), (2, 1, 2, 48, 96, 40, 4, 20.0), (3, 3, 1, 32, 16, 0, 0, 0.0),
+    (8, 2, 2, 64, 128, 100, 0, 30.0), (2, 2, 2, 24, 20, 9, 9, 5.0)])
+def test_attention_with_maps_over_shuffled_pages(dtype, H, G, M, D, DV, size, keep, cap):
+    """A portion of 150 tokens after 70 cached ones (tiles of 128 and 22 rows) and, in the same cache, single
+    tokens at several contexts, over pages handed out in a shuffled order; cache rows that no query may
+    read hold NaN.  The tensor-core kernel where it applies (bfloat16, sizes that are multiples of 16), the
+    CUDA-core kernel, and the partitioned single-token kernel with its merge, against float64."""
+    from redline_b200.ops import kernels
+    g = torch.Generator().manual_seed(H * D + DV)
+    ps, L, p0 = 16, 220, 70
+    n = L - p0
+    scale, lam, post, eps = 0.2, 0.37, 0.6, 1e-5
+    q = torch.randn(L, H, M, D, generator=g).to(dtype)
+    k = torch.randn(L, G, M, D, generator=g).to(dtype)
+    v = torch.randn(L, G, DV, generator=g).to(dtype)
+    pages = (L + ps - 1) // ps
+    perm = (torch.randperm(pages + 3, generator=g) + 1)[:pages].to(torch.int32)         # page 0 is never handed out
+    kc = torch.full((pages + 4, G * M, ps, D), float("nan"), dtype=dtype)
+    vc = torch.full((pages + 4, G, ps, DV), float("nan"), dtype=dtype)
+    for j in range(L):
+        kc[perm[j // ps], :, j % ps] = k[j].reshape(G * M, D)
+        vc[perm[j // ps], :, j % ps] = v[j]
+    if size > 0:       # what every query's window has passed (and is not kept) may hold anything: poison it
+        for j in range(keep, max(0, p0 - size + 1)):
+            kc[perm[j // ps], :, j % ps] = float("nan")
+            vc[perm[j // ps], :, j % ps] = float("nan")
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    table = torch.zeros(1, pages + 2, dtype=torch.int32)
+    table[0, :pages] = perm
+    table = table.to(DEV)
+    want = attend(q[p0:].double(), k.double(), v.double(), p0, size, keep, scale, cap, lam, post, eps, True)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    qd = q[p0:].reshape(n, -1).contiguous().to(DEV)
+    positions = torch.arange(p0, L, dtype=torch.int32, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)      # noqa: E731
+    tile_seq, tile_tok, tile_rows = i32([0, 0]), i32([0, 128]), i32([128, n - 128])
+    impls = [1] + ([2] if dtype == torch.bfloat16 and D % 16 == 0 and DV % 16 == 0 else [])
+    for impl in impls:
+        out = torch.full((n, H * DV), float("nan"), dtype=dtype, device=DEV)
+        kernels.maps_attn_prefill(qd, qd.stride(0), kc, vc, table, tile_seq, tile_tok, tile_rows, positions, out, 2,
+                                  128, H, G, D, DV, M, ps, size, keep, scale, cap, lam, post, eps, True, impl=impl)
+        assert rel(out, want) < tol, impl
+    # single tokens: the last token of contexts that end at several places (also across a 128-key partition)
+    ends = [p0 + 1, 128, 129, 130, L]
+    rows = [e - 1 - p0 for e in ends]
+    items = i32([[r, 0, e, 0] for r, e in zip(rows, ends)])
+    parts = (L + 127) // 128
+    part_o = torch.full((len(ends) * H * M * parts * DV,), float("nan"), device=DEV)
+    part_ml = torch.full((len(ends) * H * M * parts * 2,), float("nan"), device=DEV)
+    out = torch.zeros((n, H * DV), dtype=dtype, device=DEV)
+    kernels.maps_attn_decode(qd, qd.stride(0), kc, vc, table, items, part_o, part_ml, parts, out, len(ends), H, G, D, DV,
+                             M, ps, size, keep, scale, cap, lam, post, eps, True)
+    assert rel(out[rows], want[rows]) < tol

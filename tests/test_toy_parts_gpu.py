@@ -185,7 +185,7 @@ def oracle_greedy(w, table, prompt, outputs):
 def test_toy_parts_are_registered_built_loaded_and_stepped(tmp_path):
     eng, w = toy_engine(tmp_path)
     runner = eng.runner
-    assert sorted(runner.states.pools) == [0, 2] and runner.states.pools[0].shape == (3, H)
+    assert sorted(runner.states.pools) == [0, 2] and runner.states.pools[0].shape == (3 + 1, H)   # (one slot more: the padding rows')
     assert len(runner.groups) == 1 and runner.groups[0].owners == [1]
     table = runner.model.blocks[1].mixer.position.table.cpu()
     rng = np.random.RandomState(3)
