@@ -108,6 +108,13 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
   const int warp = threadIdx.x >> 5;
   const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
   const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+  // the pages of this thread's keys (key base + it * 16 + slot), read once
+  int pages[kPart / kKeysPerIter];
+#pragma unroll
+  for (int it = 0; it < kPart / kKeysPerIter; ++it) {
+    const int j = base + it * kKeysPerIter + slot;
+    pages[it] = (j < j_hi && key_visible(j, me, a.mask)) ? bt[j / a.page_size] : 0;
+  }
 
   for (int m = 0; m < kM; ++m) {
     const int khead = kvh * kM + m;
@@ -122,10 +129,11 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
       }
       __syncthreads();
       // ---- scores (every lane of a warp makes the same number of trips: the shuffles need all of them)
-      for (int jb = base; jb < j_hi; jb += kKeysPerIter) {
-        const int j = jb + slot;
+#pragma unroll
+      for (int it = 0; it < kPart / kKeysPerIter; ++it) {
+        const int j = base + it * kKeysPerIter + slot;
         const bool live = j < j_hi && key_visible(j, me, a.mask);
-        const size_t page = live ? bt[j / a.page_size] : 0;
+        const size_t page = live ? pages[it] : 0;
         const T* kp = a.kcache + ((page * (a.kv_heads * kM) + khead) * a.page_size + j % a.page_size) * kD;
         float dot[kRows];
 #pragma unroll
@@ -183,9 +191,11 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
         for (int c = 0; c < CPLV; ++c)
 #pragma unroll
           for (int e = 0; e < EVV; ++e) acc[g][c][e] = 0.f;
-      for (int j = base + slot; j < j_hi; j += kKeysPerIter) {
-        if (!key_visible(j, me, a.mask)) continue;
-        const size_t page = bt[j / a.page_size];
+#pragma unroll
+      for (int it = 0; it < kPart / kKeysPerIter; ++it) {
+        const int j = base + it * kKeysPerIter + slot;
+        if (j >= j_hi || !key_visible(j, me, a.mask)) continue;
+        const size_t page = pages[it];
         const T* vp = a.vcache + ((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV;
         float p[kRows];
 #pragma unroll
@@ -448,7 +458,8 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
 // ------------------------------------------------------------------ prompt portions on the tensor cores
 // bfloat16, key and value sizes that are multiples of 16.  One CTA of four warps takes 64 query rows of a
 // tile for one head; a warp takes 16 of them.  Keys and values come in tiles of 64 from the paged cache
-// into shared memory (16-byte pieces, rows padded by 16 bytes so that fragment reads meet no bank twice).
+// into a two-stage ring in shared memory (cp.async in 16-byte pieces, the next visible tile on its way
+// while the running one is worked on; rows padded by 16 bytes so that fragment reads meet no bank twice).
 // S = Q K^T with mma.sync.m16n8k16 (Q fragments straight from global memory, once per map), scale, cap,
 // mask and online softmax in float32 in the accumulator layout; O += P V with V fragments from
 // ldmatrix.trans.  The weights P are not cut to 16 bits: P = P_hi + P_lo (two bfloat16 operands, two MMAs
@@ -465,6 +476,10 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -480,9 +495,9 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [64][D + 8]
-  bf16* Vs = Ks + kTK * kLDK;                                    // [64][DV + 8]
-  float* O0 = reinterpret_cast<float*>(Vs + kTK * kLDV);         // [64][DV], the first map's result (two maps)
+  bf16* Kst = reinterpret_cast<bf16*>(smem_raw);                // two stages of [64][D + 8]
+  bf16* Vst = Kst + 2 * kTK * kLDK;                              // two stages of [64][DV + 8]
+  float* O0 = reinterpret_cast<float*>(Vst + 2 * kTK * kLDV);    // [64][DV], the first map's result (two maps)
 
   const int halves = a.tile_quarters;                            // 64-row parts of a tile of the launch
   const int tile = blockIdx.x / halves, part = blockIdx.x % halves, head = blockIdx.y;
@@ -498,6 +513,7 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
   const int p0 = pos0 + r0, p1 = pos0 + r1;
   const bool ok0 = r0 < rows, ok1 = r1 < rows;
   const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+  const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;      // (pages hold a power of two of tokens)
 
   float o[kDV / 8][4];
   for (int m = 0; m < kM; ++m) {
@@ -518,33 +534,52 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
     for (int nd = 0; nd < kDV / 8; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
     float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    for (int k0 = 0; k0 < k_end; k0 += kTK) {
-      const int t_hi = min(k0 + kTK, k_end);
-      if (a.mask.window > 0 && k0 >= a.mask.keep_first && t_hi <= pos0 - a.mask.window + 1) continue;
-      __syncthreads();                       // the tile before has been read by every warp
+    // the visible key tiles in turn; the next one is on its way (cp.async) while this one is worked on
+    auto next_visible = [&](int k0) {
+      while (k0 < k_end && a.mask.window > 0 && k0 >= a.mask.keep_first &&
+             min(k0 + kTK, k_end) <= pos0 - a.mask.window + 1)
+        k0 += kTK;
+      return k0;
+    };
+    auto issue = [&](int stage, int k0) {
+      bf16* Kd = Kst + stage * kTK * kLDK;
+      bf16* Vd = Vst + stage * kTK * kLDV;
       for (int i = threadIdx.x; i < kTK * (kD / 8); i += 128) {
         const int key = i / (kD / 8), c = i - key * (kD / 8);
         const int j = k0 + key;
-        uint4 v = make_uint4(0, 0, 0, 0);
+        bf16* d = Kd + key * kLDK + c * 8;
         if (j < k_end && !dead_key(j, pos0, a.mask)) {
-          const size_t page = bt[j / a.page_size];
-          v = *reinterpret_cast<const uint4*>(a.kcache + ((page * (a.kv_heads * kM) + kvh * kM + m) * a.page_size +
-                                                           j % a.page_size) * kD + c * 8);
+          const size_t page = bt[j >> ps_shift];
+          cp_async16(d, a.kcache + ((page * (a.kv_heads * kM) + kvh * kM + m) * a.page_size + (j & ps_mask)) * kD + c * 8);
+        } else {
+          *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
-        *reinterpret_cast<uint4*>(Ks + key * kLDK + c * 8) = v;
       }
       for (int i = threadIdx.x; i < kTK * (kDV / 8); i += 128) {
         const int key = i / (kDV / 8), c = i - key * (kDV / 8);
         const int j = k0 + key;
-        uint4 v = make_uint4(0, 0, 0, 0);
+        bf16* d = Vd + key * kLDV + c * 8;
         if (j < k_end && !dead_key(j, pos0, a.mask)) {
-          const size_t page = bt[j / a.page_size];
-          v = *reinterpret_cast<const uint4*>(a.vcache + ((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV +
-                                              c * 8);
+          const size_t page = bt[j >> ps_shift];
+          cp_async16(d, a.vcache + ((page * a.kv_heads + kvh) * a.page_size + (j & ps_mask)) * kDV + c * 8);
+        } else {
+          *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
-        *reinterpret_cast<uint4*>(Vs + key * kLDV + c * 8) = v;
       }
+    };
+    int stage = 0;
+    int k0 = next_visible(0);
+    __syncthreads();                         // (the map before has left both stages)
+    if (k0 < k_end) issue(0, k0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    while (k0 < k_end) {
+      const int k1 = next_visible(k0 + kTK);
+      if (k1 < k_end) issue(stage ^ 1, k1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 1;" ::: "memory");       // this tile's copies have landed
       __syncthreads();
+      const bf16* Ks = Kst + stage * kTK * kLDK;
+      const bf16* Vs = Vst + stage * kTK * kLDV;
       // ---- S = Q K^T: 16 rows x 64 keys per warp
       float s[kTK / 8][4];
 #pragma unroll
@@ -624,7 +659,11 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
           mma_16816(o[nd + 1], pl, b2, b3);
         }
       }
+      __syncthreads();                       // every warp has read this stage: the tile after the next may land in it
+      stage ^= 1;
+      k0 = k1;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -688,6 +727,12 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
 }
 #endif  // sizes that are multiples of 16
 
+
+// Whether this module's kernels have been allowed their dynamic shared memory.  File-scope statics on
+// purpose: a static inside a function template is one object for the whole process, shared by every
+// compiled variant of this file that is loaded, and a variant would then skip its own kernels.
+static bool g_mma_attr_set = false;
+static bool g_simt_attr_set[2] = {false, false};
 
 template <typename T>
 int launch_maps_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt, int max_blocks,
@@ -756,18 +801,17 @@ int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void*
   a.eps = eps;
   a.unit_norm = unit_norm;
 #ifdef RL_MAPS_HAVE_MMA
-  if (sizeof(T) == 2 && impl != 1 && q_stride % 2 == 0 && out_stride % 2 == 0 &&
+  if (sizeof(T) == 2 && impl != 1 && q_stride % 2 == 0 && out_stride % 2 == 0 && (page_size & (page_size - 1)) == 0 &&
       reinterpret_cast<uintptr_t>(q) % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0 &&
       reinterpret_cast<uintptr_t>(kc) % 16 == 0 && reinterpret_cast<uintptr_t>(vc) % 16 == 0) {
     MapsPrefillArgs<bf16> b;
     static_assert(sizeof(b) == sizeof(a), "one layout for both element types");
     memcpy(&b, &a, sizeof(b));
     b.tile_quarters = (tile_rows_max + kTQ - 1) / kTQ;
-    const size_t need = (kTK * kLDK + kTK * kLDV) * sizeof(bf16) + (kM == 2 ? kTQ * kDV * sizeof(float) : 0);
-    static bool mma_attr_set = false;
-    if (!mma_attr_set && need > 48 * 1024) {
+    const size_t need = 2 * (kTK * kLDK + kTK * kLDV) * sizeof(bf16) + (kM == 2 ? kTQ * kDV * sizeof(float) : 0);
+    if (!g_mma_attr_set && need > 48 * 1024) {
       cudaFuncSetAttribute(maps_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(need));
-      mma_attr_set = true;
+      g_mma_attr_set = true;
     }
     return static_cast<int>(launch_kernel(maps_prefill_mma_kernel, dim3(tiles * b.tile_quarters, heads), dim3(128), need,
                                           stream, b));
@@ -775,7 +819,7 @@ int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void*
 #endif
   if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);      // the tensor-core kernel was asked for
   const size_t smem = (kBQ * (kD + 1) + kBK * (kD + 1) + kBK * kDV + kBQ * (kBK + 1)) * sizeof(float);
-  static bool attr_set = false;
+  bool& attr_set = g_simt_attr_set[sizeof(T) == 2 ? 1 : 0];
   if (!attr_set && smem > 48 * 1024) {
     cudaFuncSetAttribute(maps_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     attr_set = true;

@@ -1,12 +1,12 @@
 // Routed feed-forward (mixture of experts): the router, the grouping of (token, expert) pairs by
 // expert, and the experts' two products as grouped matrix products.
 //
-//   router:   z = W_r x (float32 sums), score = sigmoid(z) (or softmax over the experts); experts lie in
+//   router:   z = W_r x (float32 sums; in this kernel, or handed in as float32 logits), score = sigmoid(z) (or softmax over the experts); experts lie in
 //             `groups` equal groups of neighbours; a group's score is the sum of its `group_top` best
 //             scores; only experts of the best `keep` groups can be chosen; the `top` best of those are
 //             the token's experts, weighted by their scores (optionally divided by their sum)
 //   pairs:    pair p = token * top + k; `order` lists the pairs expert by expert, `tile_expert` /
-//             `tile_begin` / `tile_rows` cut every expert's pairs into tiles of up to 32 rows
+//             `tile_begin` / `tile_rows` cut every expert's pairs into tiles of up to 64 rows
 //   products: up:   act[p, :]  = f(W_up[e]   x[token(p), :])      f = activation
 //             down: y[p, :]    =   W_down[e] act[p, :]
 //   combine:  out[t, :] = sum_k weight[t, k] * y[t * top + k, :] (+ shared[t, :]), k in order
@@ -14,7 +14,7 @@
 // A pair's results do not depend on which other pairs share its tile or on the order within the
 // expert's list: every output element is one thread's sum over k in a fixed order.  All sums are float32.
 // bfloat16 operands go through mma.sync (m16n8k16, float32 accumulators); float32 operands through
-// FFMA only.
+// FFMA only; steps of a handful of pairs stream the chosen experts' weights through FFMA in both types.
 #include "common.cuh"
 
 namespace rl {
@@ -66,12 +66,17 @@ __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __r
   float* gscore = work + experts;
   float* gsel = gscore + groups;
   const TA* xr = x + static_cast<size_t>(t) * ld;
-  for (int e = 0; e < experts; ++e) {
-    const TW* w = router + static_cast<size_t>(e) * width;
-    float s = 0.f;
-    for (int c = lane; c < width; c += 32) s = fmaf(to_float(xr[c]), to_float(w[c]), s);
-    s = warp_sum(s);
-    if (lane == 0) score[e] = s;
+  if (router == nullptr) {
+    // x holds the logits themselves [tokens, experts] (a matrix product before this kernel made them)
+    for (int e = lane; e < experts; e += 32) score[e] = to_float(xr[e]);
+  } else {
+    for (int e = 0; e < experts; ++e) {
+      const TW* w = router + static_cast<size_t>(e) * width;
+      float s = 0.f;
+      for (int c = lane; c < width; c += 32) s = fmaf(to_float(xr[c]), to_float(w[c]), s);
+      s = warp_sum(s);
+      if (lane == 0) score[e] = s;
+    }
   }
   __syncwarp();
   if (softmax) {
@@ -163,7 +168,7 @@ __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __r
 
 // ------------------------------------------------------------------ pairs grouped by expert
 // One CTA.  counts -> offsets -> order; then the tiles.  meta: [0] number of tiles.
-constexpr int kTileRows = 32;
+constexpr int kTileRows = 64;
 
 __global__ void moe_group_kernel(const int32_t* __restrict__ choice, int pairs, int experts,
                                  int32_t* __restrict__ order, int32_t* __restrict__ tile_expert,
@@ -213,7 +218,7 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ choice, int pairs, 
 }
 
 // ------------------------------------------------------------------ grouped products
-// One CTA per (tile of up to 32 pairs of one expert, 64 output features).  Row r of the tile is pair
+// One CTA per (tile of up to 64 pairs of one expert, 64 output features).  Row r of the tile is pair
 // order[begin + r]; its input row is src[pair / src_div] (src_div = top for the first product, whose
 // input is the token's row; 1 for the second, whose input is the pair's own row); its output row is
 // dst[pair].  W is [experts, n, k].
@@ -225,7 +230,7 @@ moe_gemm_simt_kernel(const TA* __restrict__ src, int ld_src, int src_div, const 
                      const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ meta, int act) {
   pdl_launch();
   pdl_wait();
-  constexpr int BM = kTileRows, BN = 64, BK = 32;
+  constexpr int BM = kTileRows, BN = 64, BK = 32, RPT = BM / 8;
   __shared__ float As[BM][BK + 1];
   __shared__ float Ws[BN][BK + 1];
   __shared__ int32_t pair_of[BM];
@@ -236,11 +241,11 @@ moe_gemm_simt_kernel(const TA* __restrict__ src, int ld_src, int src_div, const 
   const TW* we = w + static_cast<size_t>(e) * n * k;
   if (threadIdx.x < BM) pair_of[threadIdx.x] = threadIdx.x < rows ? order[begin + threadIdx.x] : -1;
   __syncthreads();
-  // thread (ty, tx): rows ty * 4 .. + 3 (8 groups), columns tx, tx + 16, tx + 32, tx + 48
+  // thread (ty, tx): rows ty * 8 .. + 7 (8 groups), columns tx, tx + 16, tx + 32, tx + 48
   const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
-  float acc[4][4];
+  float acc[RPT][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < RPT; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   for (int k0 = 0; k0 < k; k0 += BK) {
@@ -257,20 +262,20 @@ moe_gemm_simt_kernel(const TA* __restrict__ src, int ld_src, int src_div, const 
     __syncthreads();
 #pragma unroll 8
     for (int c = 0; c < BK; ++c) {
-      float av[4], wv[4];
+      float av[RPT], wv[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) av[i] = As[ty * 4 + i][c];
+      for (int i = 0; i < RPT; ++i) av[i] = As[ty * RPT + i][c];
 #pragma unroll
       for (int j = 0; j < 4; ++j) wv[j] = Ws[tx + 16 * j][c];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < RPT; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int p = pair_of[ty * 4 + i];
+  for (int i = 0; i < RPT; ++i) {
+    const int p = pair_of[ty * RPT + i];
     if (p < 0) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -280,23 +285,26 @@ moe_gemm_simt_kernel(const TA* __restrict__ src, int ld_src, int src_div, const 
   }
 }
 
-// The same tile on the tensor cores for bfloat16: four warps, each 16 of the 64 output features as two
-// n-tiles of 8, over both 16-row halves of the tile; A (pairs' rows) and W tiles staged in shared memory
-// as bfloat16.  mma.sync.m16n8k16, float32 accumulators, k in ascending blocks of 32.
+// The tile on the tensor cores for bfloat16: 64 pairs x 128 output features per CTA, eight warps in a
+// 2 x 4 grid (32 rows x 32 features each: 2 x 4 MMAs per 16 of k).  A (the pairs' rows) and W tiles of
+// 32 k go through shared memory as bfloat16; the next k block's 16-byte pieces are asked for before the
+// MMAs of the running one and stored after them.  mma.sync.m16n8k16, float32 accumulators, k ascending.
 __device__ __forceinline__ void mma_bf16_16816(float* d, const uint32_t* a, const uint32_t* b) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__global__ void __launch_bounds__(128)
+constexpr int kMmaCols = 128;
+
+__global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const bf16* __restrict__ src, int ld_src, int src_div, const bf16* __restrict__ w, int n, int k,
                     bf16* __restrict__ dst, int ld_dst, const int32_t* __restrict__ order,
                     const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_begin,
                     const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ meta, int act) {
   pdl_launch();
   pdl_wait();
-  constexpr int BM = kTileRows, BN = 64, BK = 32, LD = BK + 8;      // 80-byte rows: fragment reads hit distinct banks
+  constexpr int BM = kTileRows, BN = kMmaCols, BK = 32, LD = BK + 8;      // 80-byte rows: fragment reads hit distinct banks
   __shared__ __align__(16) bf16 As[BM][LD];
   __shared__ __align__(16) bf16 Ws[BN][LD];
   __shared__ int32_t pair_of[BM];
@@ -309,50 +317,59 @@ moe_gemm_mma_kernel(const bf16* __restrict__ src, int ld_src, int src_div, const
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
-  float acc[2][2][4];               // [row half][n tile][fragment]
+  const int wm = warp & 1, wn = warp >> 1;            // this warp's 32 rows and 32 features
+  float acc[2][4][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int f = 0; f < 4; ++f) acc[i][j][f] = 0.f;
+  // this thread's pieces of a k block: one of A (64 rows x 4 pieces), two of W (128 rows x 4 pieces)
+  const int ar = threadIdx.x >> 2, ac = (threadIdx.x & 3) * 8;
+  const int ap = pair_of[ar];
+  const bf16* a_src = ap >= 0 ? src + static_cast<size_t>(ap / src_div) * ld_src + ac : nullptr;
+  const bf16* w_src[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = ar + h * 64;
+    w_src[h] = n0 + r < n ? we + static_cast<size_t>(n0 + r) * k + ac : nullptr;
+  }
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 pa = zero, pw[2] = {zero, zero};
+  auto fetch = [&](int k0) {
+    const bool in = k0 + ac < k;
+    pa = (a_src != nullptr && in) ? *reinterpret_cast<const uint4*>(a_src + k0) : zero;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) pw[h] = (w_src[h] != nullptr && in) ? *reinterpret_cast<const uint4*>(w_src[h] + k0) : zero;
+  };
+  fetch(0);
   for (int k0 = 0; k0 < k; k0 += BK) {
+    __syncthreads();                                  // the block before has been read
+    *reinterpret_cast<uint4*>(&As[ar][ac]) = pa;
+    *reinterpret_cast<uint4*>(&Ws[ar][ac]) = pw[0];
+    *reinterpret_cast<uint4*>(&Ws[ar + 64][ac]) = pw[1];
     __syncthreads();
-    // 16-byte pieces: a row of 32 elements is four pieces (k is a multiple of 8)
-    for (int i = threadIdx.x; i < BM * 4; i += 128) {
-      const int r = i >> 2, c = (i & 3) * 8;
-      const int p = pair_of[r];
-      uint4 v = zero;
-      if (p >= 0 && k0 + c < k) v = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(p / src_div) * ld_src + k0 + c);
-      *reinterpret_cast<uint4*>(&As[r][c]) = v;
-    }
-    for (int i = threadIdx.x; i < BN * 4; i += 128) {
-      const int r = i >> 2, c = (i & 3) * 8;
-      uint4 v = zero;
-      if (n0 + r < n && k0 + c < k) v = *reinterpret_cast<const uint4*>(we + static_cast<size_t>(n0 + r) * k + k0 + c);
-      *reinterpret_cast<uint4*>(&Ws[r][c]) = v;
-    }
-    __syncthreads();
+    if (k0 + BK < k) fetch(k0 + BK);                  // on its way while the MMAs run
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
-      uint32_t b[2][2];
+      uint32_t b[4][2];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const bf16* wr = &Ws[warp * 16 + j * 8 + gid][kk + tig * 2];
+      for (int j = 0; j < 4; ++j) {
+        const bf16* wr = &Ws[wn * 32 + j * 8 + gid][kk + tig * 2];
         b[j][0] = *reinterpret_cast<const uint32_t*>(wr);
         b[j][1] = *reinterpret_cast<const uint32_t*>(wr + 8);
       }
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         uint32_t a[4];
-        const bf16* ar = &As[i * 16 + gid][kk + tig * 2];
-        a[0] = *reinterpret_cast<const uint32_t*>(ar);
-        a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * LD);
-        a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
-        a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * LD + 8);
+        const bf16* arow = &As[wm * 32 + i * 16 + gid][kk + tig * 2];
+        a[0] = *reinterpret_cast<const uint32_t*>(arow);
+        a[1] = *reinterpret_cast<const uint32_t*>(arow + 8 * LD);
+        a[2] = *reinterpret_cast<const uint32_t*>(arow + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(arow + 8 * LD + 8);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) mma_bf16_16816(acc[i][j], a, b[j]);
+        for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], a, b[j]);
       }
     }
   }
@@ -360,11 +377,11 @@ moe_gemm_mma_kernel(const bf16* __restrict__ src, int ld_src, int src_div, const
   for (int i = 0; i < 2; ++i)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int p = pair_of[i * 16 + gid + half * 8];
+      const int p = pair_of[wm * 32 + i * 16 + gid + half * 8];
       if (p < 0) continue;
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int col = n0 + warp * 16 + j * 8 + tig * 2;
+      for (int j = 0; j < 4; ++j) {
+        const int col = n0 + wn * 32 + j * 8 + tig * 2;
         const float v0 = moe_activate(acc[i][j][half * 2], act), v1 = moe_activate(acc[i][j][half * 2 + 1], act);
         bf16* d = dst + static_cast<size_t>(p) * ld_dst + col;
         if (col + 1 < n && (ld_dst % 2 == 0)) {
@@ -375,6 +392,86 @@ moe_gemm_mma_kernel(const bf16* __restrict__ src, int ld_src, int src_div, const
         }
       }
     }
+}
+
+// For a handful of pairs (single-token steps) the products are bound by the stream of the chosen experts'
+// weights: one CTA per (tile, 16 output features), a warp takes four features at once and streams their
+// weight rows in 16-byte pieces, up to four of the tile's rows at a time (their input rows come from L1).
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gemv_kernel(const T* __restrict__ src, int ld_src, int src_div, const T* __restrict__ w, int n, int k,
+                T* __restrict__ dst, int ld_dst, const int32_t* __restrict__ order,
+                const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_begin,
+                const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ meta, int act) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int VEC = Vec16<T>::N, NF = 4, NR = 4;
+  const int tile = blockIdx.x;
+  if (tile >= meta[0]) return;
+  const int e = tile_expert[tile], begin = tile_begin[tile], rows = tile_rows[tile];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.y * 16 + warp * NF;
+  if (f0 >= n) return;
+  const T* we = w + static_cast<size_t>(e) * n * k;
+  const bool vec = (k % VEC == 0) && (ld_src % VEC == 0) && (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(w) % 16 == 0);
+  for (int r0 = 0; r0 < rows; r0 += NR) {
+    const int nr = min(NR, rows - r0);
+    int pair[NR];
+    const T* xr[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      pair[r] = r < nr ? order[begin + r0 + r] : 0;
+      xr[r] = src + static_cast<size_t>(pair[r] / src_div) * ld_src;
+    }
+    float acc[NF][NR];
+#pragma unroll
+    for (int f = 0; f < NF; ++f)
+#pragma unroll
+      for (int r = 0; r < NR; ++r) acc[f][r] = 0.f;
+    if (vec) {
+      for (int c = lane * VEC; c < k; c += 32 * VEC) {
+        float wv[NF][VEC];
+#pragma unroll
+        for (int f = 0; f < NF; ++f) {
+          if (f0 + f < n) load16(we + static_cast<size_t>(f0 + f) * k + c, wv[f]);
+          else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) wv[f][i] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          if (r < nr) {
+            float xv[VEC];
+            load16(xr[r] + c, xv);
+#pragma unroll
+            for (int f = 0; f < NF; ++f)
+#pragma unroll
+              for (int i = 0; i < VEC; ++i) acc[f][r] = fmaf(wv[f][i], xv[i], acc[f][r]);
+          }
+        }
+      }
+    } else {
+      for (int c = lane; c < k; c += 32) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          const float xv = r < nr ? to_float(xr[r][c]) : 0.f;
+#pragma unroll
+          for (int f = 0; f < NF; ++f)
+            if (f0 + f < n) acc[f][r] = fmaf(to_float(we[static_cast<size_t>(f0 + f) * k + c]), xv, acc[f][r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int f = 0; f < NF; ++f)
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float v = warp_sum(acc[f][r]);
+        if (lane == 0 && r < nr && f0 + f < n)
+          dst[static_cast<size_t>(pair[r]) * ld_dst + f0 + f] = from_float<T>(moe_activate(v, act));
+      }
+  }
 }
 
 // ------------------------------------------------------------------ combine
@@ -428,12 +525,25 @@ int rl_moe_group(const int32_t* choice, int pairs, int experts, int32_t* order, 
   RL_LAUNCH_END();
 }
 
-// max_tiles: the most tiles the grouping can have made (pairs / 32 + experts); CTAs beyond the real
-// number leave at once.
+// max_tiles: the most tiles the grouping can have made (pairs / 64 + experts); CTAs beyond the real
+// number leave at once.  few_pairs: the weight-streaming kernel for a handful of pairs (single-token steps).
 int rl_moe_gemm(int act_dtype, const void* src, int ld_src, int src_div, const void* w, int n, int k, void* dst,
                 int ld_dst, const int32_t* order, const int32_t* tile_expert, const int32_t* tile_begin,
-                const int32_t* tile_rows, const int32_t* meta, int max_tiles, int act, cudaStream_t stream) {
+                const int32_t* tile_rows, const int32_t* meta, int max_tiles, int few_pairs, int act,
+                cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
+  if (few_pairs) {
+    dim3 g(max_tiles, (n + 15) / 16);
+    if (act_dtype == 0)
+      launch_kernel(moe_gemv_kernel<float>, g, dim3(128), 0, stream, static_cast<const float*>(src), ld_src, src_div,
+                    static_cast<const float*>(w), n, k, static_cast<float*>(dst), ld_dst, order, tile_expert, tile_begin,
+                    tile_rows, meta, act);
+    else
+      launch_kernel(moe_gemv_kernel<bf16>, g, dim3(128), 0, stream, static_cast<const bf16*>(src), ld_src, src_div,
+                    static_cast<const bf16*>(w), n, k, static_cast<bf16*>(dst), ld_dst, order, tile_expert, tile_begin,
+                    tile_rows, meta, act);
+    RL_LAUNCH_END();
+  }
   dim3 grid(max_tiles, (n + 63) / 64);
   if (act_dtype == 0) {
     launch_kernel(moe_gemm_simt_kernel<float, float>, grid, dim3(128), 0, stream, static_cast<const float*>(src),
@@ -441,7 +551,8 @@ int rl_moe_gemm(int act_dtype, const void* src, int ld_src, int src_div, const v
                   tile_expert, tile_begin, tile_rows, meta, act);
   } else if (k % 8 == 0 && ld_src % 8 == 0 && (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
              (reinterpret_cast<uintptr_t>(w) % 16 == 0)) {
-    launch_kernel(moe_gemm_mma_kernel, grid, dim3(128), 0, stream, static_cast<const bf16*>(src), ld_src, src_div,
+    launch_kernel(moe_gemm_mma_kernel, dim3(max_tiles, (n + kMmaCols - 1) / kMmaCols), dim3(256), 0, stream,
+                  static_cast<const bf16*>(src), ld_src, src_div,
                   static_cast<const bf16*>(w), n, k, static_cast<bf16*>(dst), ld_dst, order, tile_expert, tile_begin,
                   tile_rows, meta, act);
   } else {

@@ -90,10 +90,25 @@ __global__ void sandwich_norm_kernel(float* __restrict__ residual, const TA* __r
 
 // ------------------------------------------------ x[r, c] = act(x[r, c] + bias[c]) for c < cols
 template <typename TA>
-__global__ void bias_act_kernel(TA* __restrict__ x, int ld, const float* __restrict__ bias, int cols, int mode) {
+__global__ void bias_act_kernel(TA* __restrict__ x, int ld, const float* __restrict__ bias, int cols, int mode,
+                                int vec_ok) {
   pdl_launch();
   pdl_wait();
   TA* p = x + static_cast<size_t>(blockIdx.y) * ld;
+  constexpr int VEC = Vec16<TA>::N;
+  if (vec_ok) {      // rows start on 16-byte boundaries and cols is a multiple of the piece
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC; c < cols; c += gridDim.x * blockDim.x * VEC) {
+      float v[VEC];
+      load16(p + c, v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        if (bias != nullptr) v[i] = to_float(from_float<TA>(v[i] + bias[c + i]));
+        v[i] = activate(v[i], mode);
+      }
+      store16(p + c, v);
+    }
+    return;
+  }
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
     float v = to_float(p[c]);
     if (bias != nullptr) v = to_float(from_float<TA>(v + bias[c]));   // (the biased projection is what is stored)
@@ -177,11 +192,14 @@ int rl_sandwich_norm(float* residual, const void* delta, int ld_delta, const voi
 int rl_bias_act(void* x, int act_dtype, int ld, const float* bias, int rows, int cols, int mode, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   const int th = 256;
-  dim3 grid(min((cols + th - 1) / th, 64), rows);
+  const int vec = act_dtype == RL_F32 ? 4 : 8;
+  const int vec_ok = (cols % vec == 0 && ld % vec == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0) ? 1 : 0;
+  const int per_thread = vec_ok ? vec : 1;
+  dim3 grid(min((cols + th * per_thread - 1) / (th * per_thread), 64), rows);
   if (act_dtype == RL_F32)
-    launch_kernel(bias_act_kernel<float>, grid, dim3(th), 0, stream, static_cast<float*>(x), ld, bias, cols, mode);
+    launch_kernel(bias_act_kernel<float>, grid, dim3(th), 0, stream, static_cast<float*>(x), ld, bias, cols, mode, vec_ok);
   else
-    launch_kernel(bias_act_kernel<bf16>, grid, dim3(th), 0, stream, static_cast<bf16*>(x), ld, bias, cols, mode);
+    launch_kernel(bias_act_kernel<bf16>, grid, dim3(th), 0, stream, static_cast<bf16*>(x), ld, bias, cols, mode, vec_ok);
   RL_LAUNCH_END();
 }
 

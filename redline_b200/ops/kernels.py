@@ -745,26 +745,34 @@ def _moe() -> ctypes.CDLL:
     return _lib("moe", "moe.cu")
 
 
-MOE_TILE_ROWS = 32
+MOE_TILE_ROWS = 64
+MOE_FEW_PAIRS = 64        # up to so many (token, expert) pairs the products stream the weights per pair
 
 
 def moe_max_tiles(pairs: int, experts: int) -> int:
     return pairs // MOE_TILE_ROWS + experts
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, choice: torch.Tensor, weight: torch.Tensor, tokens: int,
+def moe_route(x: torch.Tensor, router: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor, tokens: int,
               groups: int, keep: int, group_top: int, top: int, softmax: bool = False, renorm: bool = False) -> None:
     """Per token: scores of the experts (float32 sums; sigmoid, or softmax), the best ``keep`` of ``groups``
     groups of neighbouring experts by the sum of their ``group_top`` best scores, the ``top`` best experts
-    of those into choice [tokens, top] int32 with their scores in weight [tokens, top] float32."""
+    of those into choice [tokens, top] int32 with their scores in weight [tokens, top] float32.  With
+    ``router`` None, ``x`` holds the logits themselves, float32 [tokens, experts]."""
     _need_cuda(x, router, choice, weight)
-    experts, width = router.shape
+    if router is None:
+        if x.dtype != torch.float32:
+            raise KernelError("moe_route: logits handed in must be float32")
+        experts, width = x.shape[1], 0
+    else:
+        experts, width = router.shape
     if experts % max(groups, 1) != 0 or choice.dtype != torch.int32 or weight.dtype != torch.float32 \
-            or x.stride(1) != 1 or not router.is_contiguous():
+            or x.stride(1) != 1 or (router is not None and not router.is_contiguous()):
         raise KernelError("moe_route: experts must divide into the groups; choice int32, weight float32")
     f = _fn(_moe(), "rl_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
-    _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(router), _code(router.dtype), tokens, width, experts,
+    _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(router), _code(router.dtype) if router is not None else 0,
+             tokens, width, experts,
              max(groups, 1), keep, group_top, top, 1 if softmax else 0, 1 if renorm else 0, _ptr(choice), _ptr(weight),
              _stream()), "moe_route")
 
@@ -772,7 +780,7 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, choice: torch.Tensor, weigh
 def moe_group(choice: torch.Tensor, pairs: int, experts: int, order: torch.Tensor, tile_expert: torch.Tensor,
               tile_begin: torch.Tensor, tile_rows: torch.Tensor, meta: torch.Tensor) -> None:
     """Lists the (token, slot) pairs expert by expert (``order``) and cuts every expert's list into tiles of
-    up to 32 pairs (``tile_*``, their number in meta[0]); all int32, the tile lists ``moe_max_tiles`` long."""
+    up to 64 pairs (``tile_*``, their number in meta[0]); all int32, the tile lists ``moe_max_tiles`` long."""
     _need_cuda(choice, order, tile_expert, tile_begin, tile_rows, meta)
     f = _fn(_moe(), "rl_moe_group", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(choice), pairs, experts, _ptr(order), _ptr(tile_expert), _ptr(tile_begin), _ptr(tile_rows),
@@ -781,18 +789,22 @@ def moe_group(choice: torch.Tensor, pairs: int, experts: int, order: torch.Tenso
 
 def moe_gemm(src: torch.Tensor, src_div: int, w: torch.Tensor, dst: torch.Tensor, order: torch.Tensor,
              tile_expert: torch.Tensor, tile_begin: torch.Tensor, tile_rows: torch.Tensor, meta: torch.Tensor,
-             max_tiles: int, act: int = ACT_NONE) -> None:
+             max_tiles: int, act: int = ACT_NONE, few_pairs: Optional[bool] = None) -> None:
     """dst[pair] = act(w[expert of the pair] @ src[pair // src_div]) for every listed pair: w [experts, n, k]
-    (or [experts * n, k]) with ``n = dst.shape[1]``, src [*, k], dst [pairs, n]."""
+    (or [experts * n, k]) with ``n = dst.shape[1]``, src [*, k], dst [pairs, n].  ``few_pairs`` chooses the
+    kernel that streams the weights for a handful of pairs (default: up to MOE_FEW_PAIRS rows of dst)."""
     _need_cuda(src, w, dst)
     n, k = dst.shape[1], src.shape[1]
     if w.shape[-1] != k or not w.is_contiguous() or src.stride(1) != 1 or dst.stride(1) != 1 or src.dtype != dst.dtype \
             or w.dtype != src.dtype:
         raise KernelError(f"moe_gemm: shapes src{tuple(src.shape)} w{tuple(w.shape)} dst{tuple(dst.shape)}, one type")
     f = _fn(_moe(), "rl_moe_gemm", [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
-                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    if few_pairs is None:
+        few_pairs = dst.shape[0] <= MOE_FEW_PAIRS
     _check(f(_code(src.dtype), _ptr(src), src.stride(0), src_div, _ptr(w), n, k, _ptr(dst), dst.stride(0), _ptr(order),
-             _ptr(tile_expert), _ptr(tile_begin), _ptr(tile_rows), _ptr(meta), max_tiles, act, _stream()), "moe_gemm")
+             _ptr(tile_expert), _ptr(tile_begin), _ptr(tile_rows), _ptr(meta), max_tiles, 1 if few_pairs else 0, act,
+             _stream()), "moe_gemm")
 
 
 def moe_combine(y: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor,

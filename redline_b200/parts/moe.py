@@ -145,7 +145,10 @@ class RoutedExperts(FeedForward):
         tile_begin = ws.get("moe.tile_begin", (cap_tiles,), torch.int32)
         tile_rows = ws.get("moe.tile_rows", (cap_tiles,), torch.int32)
         meta = ws.get("moe.meta", (4,), torch.int32)
-        kernels.moe_route(x, self.w_router, choice, weight, T, p.groups, p.group_keep, p.group_top, p.top,
+        # the router's logits as a matrix product with float32 sums and a float32 result, then the choice
+        logits = ws.get("moe.logits", (rt.max_tokens, p.num_experts), torch.float32)[:T]
+        linear(x, self.w_router, logits)
+        kernels.moe_route(logits, None, choice, weight, T, p.groups, p.group_keep, p.group_top, p.top,
                           softmax=p.score == "softmax", renorm=p.renormalize)
         kernels.moe_group(choice, pairs, p.num_experts, order, tile_expert, tile_begin, tile_rows, meta)
         op_mark(ctx, "route", self.w_router, T)

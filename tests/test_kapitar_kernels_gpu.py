@@ -183,9 +183,9 @@ def test_experts_with_the_routing_given(dtype, tol, T, E, top, W, ff):
     down = (torch.randn(E, W, ff, generator=g) / math.sqrt(ff)).to(dtype)
     shared = torch.randn(T, W, generator=g).to(dtype)
     choice = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(T)]).to(torch.int32)   # expert E-1: none
-    if T > 40:
-        choice[:40, 0] = 0                                                                               # expert 0: > 32 pairs
-        for t in range(40):
+    if T >= 70:
+        choice[:70, 0] = 0                                                                               # expert 0: more than a tile of pairs
+        for t in range(70):
             if (choice[t, 1:] == 0).any():
                 choice[t, 1:][choice[t, 1:] == 0] = E - 1
     weight = torch.rand(T, top, generator=g)
@@ -209,18 +209,22 @@ def test_experts_with_the_routing_given(dtype, tol, T, E, top, W, ff):
     kernels.moe_group(choice.to(DEV).reshape(-1), pairs, E, order, te, tb, trw, meta)
     n_tiles = int(meta[0])
     counts = torch.bincount(choice.reshape(-1).long(), minlength=E)
-    assert n_tiles == int(((counts + 31) // 32).sum())
+    assert n_tiles == int(((counts + 63) // 64).sum())
     assert sorted(order.cpu().tolist()) == list(range(pairs))
     listed = choice.reshape(-1)[order.cpu().long()]
     assert torch.equal(listed, listed.sort().values)                    # expert by expert
     act = torch.full((pairs, ff), float("nan"), dtype=dtype, device=DEV)
     y = torch.full((pairs, W), float("nan"), dtype=dtype, device=DEV)
     xd = x.to(DEV)
-    kernels.moe_gemm(xd, top, up.to(DEV).reshape(E * ff, W), act, order, te, tb, trw, meta, tiles, act=kernels.ACT_GELU_ERF)
-    kernels.moe_gemm(act, 1, down.to(DEV).reshape(E * W, ff), y, order, te, tb, trw, meta, tiles)
-    out = torch.empty(T, W, dtype=dtype, device=DEV)
-    kernels.moe_combine(y, weight.to(DEV), shared.to(DEV), out, T, top)
-    assert rel(out, want) < tol
+    for few in (False, True):          # the tiled products, and the ones that stream the weights pair by pair
+        act.fill_(float("nan"))
+        y.fill_(float("nan"))
+        kernels.moe_gemm(xd, top, up.to(DEV).reshape(E * ff, W), act, order, te, tb, trw, meta, tiles,
+                         act=kernels.ACT_GELU_ERF, few_pairs=few)
+        kernels.moe_gemm(act, 1, down.to(DEV).reshape(E * W, ff), y, order, te, tb, trw, meta, tiles, few_pairs=few)
+        out = torch.empty(T, W, dtype=dtype, device=DEV)
+        kernels.moe_combine(y, weight.to(DEV), shared.to(DEV), out, T, top)
+        assert rel(out, want) < tol, few
 
 
 def attend(q, k, v, pos0, size, keep, scale, cap, lam, post, eps, unit):
