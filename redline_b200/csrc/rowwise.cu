@@ -88,6 +88,76 @@ __global__ void sandwich_norm_kernel(float* __restrict__ residual, const TA* __r
     o[c] = from_float<TA>((row[c] - mean) * rstd * to_float(pre_w[c]));
 }
 
+// The same for rows of up to EPT x blockDim elements, the row in registers: every global load (addend,
+// stream, both weights) is asked for before the first sum, so that a row costs one round trip to memory
+// and four block reductions.  Thread t holds elements t, t + blockDim, ...
+template <typename TA, typename TW, int EPT>
+__global__ void sandwich_norm_reg_kernel(float* __restrict__ residual, const TA* __restrict__ delta, int ld_delta,
+                                         const TW* __restrict__ post_w, const TW* __restrict__ pre_w,
+                                         TA* __restrict__ out, int ld_out, const int32_t* __restrict__ rows_idx,
+                                         int hidden, float eps, int kind) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows_idx ? rows_idx[r] : r;
+  float* res = residual + static_cast<size_t>(src) * hidden;
+  const float inv_n = 1.f / static_cast<float>(hidden);
+  float v[EPT], d[EPT], pw[EPT], nw[EPT];
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    const bool in = c < hidden;
+    v[i] = in ? res[c] : 0.f;
+    d[i] = (in && delta != nullptr) ? to_float(delta[static_cast<size_t>(src) * ld_delta + c]) : 0.f;
+    pw[i] = (in && post_w != nullptr) ? to_float(post_w[c]) : 0.f;
+    nw[i] = (in && out != nullptr) ? to_float(pre_w[c]) : 0.f;
+  }
+  if (delta != nullptr) {
+    if (post_w == nullptr) {
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) v[i] += d[i];
+    } else {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) s += d[i];
+      const float mean = kind == 0 ? block_sum(s, scratch) * inv_n : 0.f;
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) {
+        const float x = (threadIdx.x + i * blockDim.x < hidden) ? d[i] - mean : 0.f;
+        q += x * x;
+      }
+      const float rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) v[i] += (d[i] - mean) * rstd * pw[i];
+    }
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < hidden) res[c] = v[i];
+    }
+  }
+  if (out == nullptr) return;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) s += v[i];
+  const float mean = kind == 0 ? block_sum(s, scratch) * inv_n : 0.f;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const float x = (threadIdx.x + i * blockDim.x < hidden) ? v[i] - mean : 0.f;
+    q += x * x;
+  }
+  const float rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+  TA* o = out + static_cast<size_t>(r) * ld_out;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < hidden) o[c] = from_float<TA>((v[i] - mean) * rstd * nw[i]);
+  }
+}
+
 // ------------------------------------------------ x[r, c] = act(x[r, c] + bias[c]) for c < cols
 template <typename TA>
 __global__ void bias_act_kernel(TA* __restrict__ x, int ld, const float* __restrict__ bias, int cols, int mode,
@@ -172,6 +242,19 @@ int rl_sandwich_norm(float* residual, const void* delta, int ld_delta, const voi
                      int w_dtype, void* out, int ld_out, int act_dtype, const int32_t* rows_idx, int rows, int hidden,
                      float eps, int kind, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  constexpr int EPT = 4;
+  if (hidden <= EPT * 1024) {                      // the row fits the registers of one CTA
+    const int th = min(1024, max(64, ((hidden + EPT - 1) / EPT + 31) / 32 * 32));
+#define RL_REG_CASE(TA, TW)                                                                                       \
+  launch_kernel(sandwich_norm_reg_kernel<TA, TW, EPT>, dim3(rows), dim3(th), 0, stream, residual,                \
+                static_cast<const TA*>(delta), ld_delta, static_cast<const TW*>(post_w),                         \
+                static_cast<const TW*>(pre_w), static_cast<TA*>(out), ld_out, rows_idx, hidden, eps, kind)
+    if (act_dtype == RL_F32) RL_REG_CASE(float, float);
+    else if (w_dtype == RL_F32) RL_REG_CASE(bf16, float);
+    else RL_REG_CASE(bf16, bf16);
+#undef RL_REG_CASE
+    RL_LAUNCH_END();
+  }
   const int th = hidden >= 2048 ? 512 : 256;
   const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
 #define RL_CASE(TA, TW)                                                                                          \

@@ -21,7 +21,7 @@ def rel(a, b):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("hidden", [96, 320, 2500])
+@pytest.mark.parametrize("hidden", [96, 320, 2500, 4100])     # (4,100: beyond the rows the register kernel takes)
 def test_norms_around_a_sublayer(dtype, tol, hidden):
     from redline_b200.ops import kernels
     g = torch.Generator().manual_seed(hidden)
