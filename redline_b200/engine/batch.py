@@ -154,6 +154,7 @@ class StepContext:
     hand_out: Optional[object] = None          # what the running part leaves
     block_next_norm: Optional[object] = None   # set by the model: the first norm of the block after this one
     block_hand: Optional[object] = None        # carried from a block's last part to the next block
+    block_normed: Optional[object] = None      # (norm, rows): a block's last kernel has already applied the next block's first norm
 
 
 @dataclass

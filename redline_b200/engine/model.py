@@ -153,7 +153,7 @@ class DecoderModel:
         op_mark(ctx, "embed", nbytes=T * self.spec.hidden_size * (4.0 + (2 if rt.dtype == torch.bfloat16 else 4)))
         pending = None
         order = self.spec.order
-        ctx.block_hand = None
+        ctx.block_hand = ctx.block_normed = None
         for i, call in enumerate(order):
             # (the block after this one may take over its first norm from this block's last kernel)
             ctx.block_next_norm = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) else None
@@ -162,7 +162,7 @@ class DecoderModel:
             pending = self.blocks[call.layer].forward(residual, pending, ctx, caches[i], states[i])
             if self.nvtx_layers:
                 torch.cuda.nvtx.range_pop()
-        ctx.block_hand = ctx.block_next_norm = None
+        ctx.block_hand = ctx.block_next_norm = ctx.block_normed = None
         head_w = getattr(self.head, "weight", None)
         if R > 0 and pending is None and self.head.forward_from(residual, self.final_norm, ctx.logit_rows, R, logits):
             op_mark(ctx, "final_norm+lm_head", head_w, R, nbytes=R * logits.shape[1] * 2.0)

@@ -75,7 +75,9 @@ class SandwichBlock(Block):
     """h += norm_1b(mixer(norm_1(h))); h += norm_2b(ffn(norm_2(h))): every sublayer's input AND output is
     normed.  ``mixer_post_norm`` / ``ffn_post_norm`` are set by the model builder from the layer's spec.
     The add of a sublayer's normed output and the input norm of the sublayer after it are one kernel
-    (``add_post_norm``); the block leaves nothing pending."""
+    (``add_post_norm``), also across blocks: the block's last kernel norms the stream for the first norm of
+    the block after it (``ctx.block_next_norm``) and leaves the result in ``ctx.block_normed``, which that
+    block takes instead of running its first norm.  The block leaves nothing pending."""
 
     mixer_post_norm = None
     ffn_post_norm = None
@@ -83,22 +85,37 @@ class SandwichBlock(Block):
     def parts(self):
         return super().parts() + [p for p in (self.mixer_post_norm, self.ffn_post_norm) if p is not None]
 
+    def first_norm(self):
+        return self.mixer_norm
+
     def forward(self, residual, pending, ctx, cache, state):
         rt = self.rt
         T = ctx.T
         ctx.block_hand = None
+        ready, ctx.block_normed = ctx.block_normed, None
         x = rt.workspace.get("block.normed", (rt.max_tokens, residual.shape[1]), rt.dtype)[:T]
-        self.mixer_norm.add_norm(residual, pending, x, rows=T)
-        op_mark(ctx, "add+norm", nbytes=PreNormBlock._norm_bytes(residual, pending, x))
+        if not (pending is None and ready is not None and ready[0] is self.mixer_norm):
+            self.mixer_norm.add_norm(residual, pending, x, rows=T)
+            op_mark(ctx, "add+norm", nbytes=PreNormBlock._norm_bytes(residual, pending, x))
         a = self.mixer.forward(x, ctx, cache, state)
         if self.ffn is None:
-            self.mixer_post_norm.add_post_norm(residual, a, None, None, rows=T)
-            op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, a, x))
+            self._last(self.mixer_post_norm, residual, a, x, ctx)
             return None
         if not self.mixer_post_norm.add_post_norm(residual, a, self.ffn_norm, x, rows=T):
             self.ffn_norm.add_norm(residual, None, x, rows=T)
         op_mark(ctx, "post_norm+add+norm", nbytes=PreNormBlock._norm_bytes(residual, a, x))
         f = self.ffn.forward(x, ctx)
-        self.ffn_post_norm.add_post_norm(residual, f, None, None, rows=T)
-        op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, f, x))
+        self._last(self.ffn_post_norm, residual, f, x, ctx)
         return None
+
+    def _last(self, post_norm, residual, delta, x, ctx) -> None:
+        """The block's last kernel: the normed add, and with it the first norm of the block after this one
+        when that norm can share the kernel (x, this block's input buffer, is free by now)."""
+        nxt = ctx.block_next_norm
+        if nxt is not None and post_norm.add_post_norm(residual, delta, nxt, x, rows=ctx.T):
+            ctx.block_normed = (nxt, x)
+            op_mark(ctx, "post_norm+add+norm", nbytes=PreNormBlock._norm_bytes(residual, delta, x))
+            return
+        if nxt is None:
+            post_norm.add_post_norm(residual, delta, None, None, rows=ctx.T)
+        op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, delta, x))
