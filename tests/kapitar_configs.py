@@ -64,6 +64,20 @@ LIGHT = {
 }
 
 
+# Sizes that are multiples of neither 8 nor 16: the kernels' 16-byte and tensor-core forms do not apply and
+# their plain forms must take over (also in the products).
+ODD = {
+    "architecture": "Kapitar", "vocab": 77, "width": 100, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": attention(3, 1, 20, 12, 9, 2, 15.0, 0.25), "mlp": moe(6, 2, 3, 2, 28, 36)},
+        {"type": "lightning", "mixer": lightning(2, 10, 20, (0.7, 0.98)), "mlp": dense(84)},
+        {"type": "attention", "mixer": attention(2, 2, 8, 4, 300, 0, 50.0, 0.7), "mlp": None},
+    ],
+}
+ODD_PLAIN = copy.deepcopy(ODD)
+ODD_PLAIN["layers"][0]["mlp"] = dense(52)
+
+
 def one_attention_layer(size, keep_first, heads=2, kv_heads=1, dim=32, vdim=32, softcap=40.0, diff=0.3, vocab=64, width=64):
     """A single attention layer without a feed-forward: what a position sees decides its logits."""
     return {"architecture": "Kapitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
@@ -71,4 +85,4 @@ def one_attention_layer(size, keep_first, heads=2, kv_heads=1, dim=32, vdim=32, 
                         "mlp": None}]}
 
 
-ALL = {"mix": MIX, "plain": PLAIN, "attn": ATTN, "light": LIGHT}
+ALL = {"mix": MIX, "plain": PLAIN, "attn": ATTN, "light": LIGHT, "odd": ODD, "odd_plain": ODD_PLAIN}

@@ -305,6 +305,22 @@ def test_lightning_layers_only(dtype, tmp_path):
     check(np.concatenate(outs), cfg, w, toks, dtype, ref=ref)
 
 
+@pytest.mark.parametrize("name,dtype", [("odd", "float32"), ("odd_plain", "bfloat16")])
+def test_sizes_that_are_no_multiples_of_8(name, dtype, models, engines):
+    """Width 100, key sizes 20 and 8, value sizes 12 and 4, an expert width of 28: no 16-byte pieces, no tensor-core
+    tiles; a prompt in portions, then single tokens."""
+    eng, (_, w) = engines(name, dtype), models[name, dtype]
+    cfg = C.ALL[name]
+    toks = random_tokens(cfg["vocab"], 90, 21)
+    ref = Reference(cfg, w, toks, dtype)
+    outs, i = [], 0
+    for s in (40, 2, 17, 1, 1, 29):
+        outs.append(eng.step_tokens([("o", toks[i:i + s], list(range(s)))]).cpu().numpy())
+        i += s
+    eng.close_request("o")
+    check(np.concatenate(outs), cfg, w, toks, dtype, ref=ref)
+
+
 def test_attention_layers_only_decode_as_cuda_graphs(models, tmp_path):
     """Without a state-keeping layer single-token steps are padded and replayed as CUDA graphs."""
     cfg = C.ATTN

@@ -172,7 +172,8 @@ def test_router(dtype, E, groups, keep, top):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("T,E,top,W,ff", [(70, 8, 3, 96, 40), (5, 16, 4, 64, 24), (300, 4, 2, 72, 100), (1, 6, 1, 40, 8)])
+@pytest.mark.parametrize("T,E,top,W,ff", [(70, 8, 3, 96, 40), (5, 16, 4, 64, 24), (300, 4, 2, 72, 100), (1, 6, 1, 40, 8),
+                                          (70, 8, 3, 100, 28)])     # (the last: no 16-byte pieces, no tensor-core tiles)
 def test_experts_with_the_routing_given(dtype, tol, T, E, top, W, ff):
     """Pairs listed expert by expert in tiles, both grouped products and the weighted sum, against the
     plain expert applied pair by pair.  Some experts get no token, one gets more than a tile."""
