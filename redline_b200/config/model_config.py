@@ -373,3 +373,169 @@ class KapitarConfig(ModelConfig):
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids)
         return out
+
+
+# ------------------------------------------------------------------------------------ Pufevik
+
+@dataclass(frozen=True)
+class PufevikRotation:
+    base: float
+    dims: int                 # the first so many entries of every head are rotated
+
+
+@dataclass(frozen=True)
+class PufevikAttention:
+    """Softmax attention of a Pufevik layer.  ``window`` 0: every earlier key (the 'attention' mixer, whose
+    queries and keys are normed per head and whose gate is one number per output entry); > 0: a sliding window
+    (the left side of a 'parallel' mixer: norms over the whole projection, a sink, one gate per head)."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[PufevikRotation]
+    window: int = 0
+    v_mix: bool = False
+
+
+@dataclass(frozen=True)
+class PufevikMemory:
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+
+@dataclass(frozen=True)
+class PufevikParallel:
+    left: PufevikAttention
+    right: PufevikMemory
+    left_scale: float
+    right_scale: float
+
+
+@dataclass(frozen=True)
+class PufevikLayer:
+    type: str                 # attention | parallel
+    mixer: Any
+    ff: int                   # width of the dense feed-forward; 0: the layer has none
+
+
+@dataclass(frozen=True)
+class PufevikConfig(ModelConfig):
+    """``Pufevik``: a decoder whose sublayers read the residual stream itself and whose outputs are RMS-normed
+    before they are added.  Mixers: gated softmax attention with normed, partly rotated queries and keys and
+    values blended with those of the first such layer; or a pair side by side, windowed attention with a sink
+    beside a matrix memory with exponential gates.  Feed-forwards are dense and gated (tanh GELU).  The
+    embedding is multiplied by a constant; the head has a matrix of its own.  config.json lists the layers one
+    by one under ``layers``."""
+
+    norm_eps: float = 1e-6
+    embedding_scale: float = 1.0
+    layers: Tuple[PufevikLayer, ...] = ()
+    raw: Optional[Dict[str, Any]] = field(default=None, compare=False, repr=False)
+
+    @staticmethod
+    def _attention(m: Dict[str, Any], where: str) -> PufevikAttention:
+        rot = m.get("rot")
+        mask = m.get("mask") or {}
+        heads = int(_need(m, "heads", where))
+        return PufevikAttention(
+            heads=heads, kv_heads=int(m.get("kv_heads") or heads), dim=int(_need(m, "dim", where)),
+            vdim=int(_need(m, "vdim", where)), scale=float(_need(m, "scale", where)),
+            rot=PufevikRotation(float(_need(rot, "base", where + ".rot")), int(_need(rot, "dims", where + ".rot")))
+            if rot else None,
+            window=int(mask.get("size", 0)), v_mix=bool(m.get("v_mix", False)))
+
+    @classmethod
+    def from_hf(cls, cfg: Dict[str, Any], model_dir: Optional[str] = None) -> "PufevikConfig":
+        layers: List[PufevikLayer] = []
+        for i, entry in enumerate(_need(cfg, "layers")):
+            where = f"layers[{i}]"
+            kind = _need(entry, "type", where)
+            m = _need(entry, "mixer", where)
+            if kind == "attention":
+                mixer: Any = cls._attention(m, where + ".mixer")
+            elif kind == "parallel":
+                r = _need(m, "right", where + ".mixer")
+                rw = where + ".mixer.right"
+                mixer = PufevikParallel(
+                    left=cls._attention(_need(m, "left", where + ".mixer"), where + ".mixer.left"),
+                    right=PufevikMemory(int(_need(r, "heads", rw)), int(_need(r, "dim", rw)), int(_need(r, "vdim", rw)),
+                                        float(_need(r, "gate_cap", rw))),
+                    left_scale=float(_need(m, "left_scale", where + ".mixer")),
+                    right_scale=float(_need(m, "right_scale", where + ".mixer")))
+            else:
+                raise ConfigError(f"{where}: mixer type '{kind}' is not supported (attention, parallel)")
+            mlp = entry.get("mlp")
+            ff = 0
+            if mlp is not None:
+                if _need(mlp, "kind", where + ".mlp") != "dense":
+                    raise ConfigError(f"{where}.mlp: kind '{mlp['kind']}' is not supported (dense)")
+                ff = int(_need(mlp, "ff", where + ".mlp"))
+            layers.append(PufevikLayer(kind, mixer, ff))
+        eos = cfg.get("eos_token_id")
+        eos = [] if eos is None else ([eos] if isinstance(eos, int) else list(eos))
+        bos = cfg.get("bos_token_id")
+        c = cls(architecture="Pufevik", vocab_size=int(_need(cfg, "vocab")), hidden_size=int(_need(cfg, "width")),
+                max_position_embeddings=int(cfg.get("max_positions", 1 << 30)),
+                bos_token_id=int(bos) if bos is not None else -1, eos_token_ids=tuple(int(e) for e in eos),
+                norm_eps=float(_need(_need(cfg, "norm"), "eps", "norm")),
+                embedding_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)), layers=tuple(layers), raw=dict(cfg))
+        c.validate()
+        return c
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
+            raise ConfigError("vocab, width and the number of layers must be positive")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        shared = None
+        for i, layer in enumerate(self.layers):
+            att = layer.mixer if layer.type == "attention" else layer.mixer.left
+            if att.heads <= 0 or att.kv_heads <= 0 or att.heads % att.kv_heads != 0 or att.dim <= 0 or att.vdim <= 0:
+                raise ConfigError(f"layers[{i}]: heads must be a positive multiple of kv_heads, dim and vdim positive")
+            if att.rot is not None and (att.rot.dims <= 0 or att.rot.dims % 2 != 0 or att.rot.dims > att.dim):
+                raise ConfigError(f"layers[{i}]: rot.dims must be even and at most dim")
+            if att.window < 0 or layer.ff < 0:
+                raise ConfigError(f"layers[{i}]: mask.size and mlp.ff must not be negative")
+            if layer.type == "attention" and att.v_mix:
+                if shared is not None and shared != att.kv_heads * att.vdim:
+                    raise ConfigError(f"layers[{i}]: layers with v_mix must have values of one size")
+                shared = att.kv_heads * att.vdim
+            if layer.type == "parallel":
+                r = layer.mixer.right
+                if r.heads <= 0 or r.dim <= 0 or r.vdim <= 0 or not r.gate_cap > 0:
+                    raise ConfigError(f"layers[{i}].mixer.right: heads, dim, vdim and gate_cap must be positive")
+
+    def to_hf(self) -> Dict[str, Any]:
+        def attention(a: PufevikAttention, parallel: bool) -> Dict[str, Any]:
+            out: Dict[str, Any] = {"heads": a.heads, "kv_heads": a.kv_heads, "dim": a.dim, "vdim": a.vdim, "scale": a.scale}
+            if a.rot is not None:
+                out["rot"] = {"base": a.rot.base, "dims": a.rot.dims}
+            if parallel:
+                out["mask"] = {"size": a.window}
+            else:
+                out["v_mix"] = a.v_mix
+            return out
+
+        layers = []
+        for layer in self.layers:
+            m = layer.mixer
+            if layer.type == "attention":
+                mixer = attention(m, False)
+            else:
+                mixer = {"left": attention(m.left, True), "left_scale": m.left_scale,
+                         "right": {"heads": m.right.heads, "dim": m.right.dim, "vdim": m.right.vdim,
+                                   "gate_cap": m.right.gate_cap},
+                         "right_scale": m.right_scale}
+            layers.append({"type": layer.type, "mixer": mixer,
+                           "mlp": {"kind": "dense", "ff": layer.ff} if layer.ff > 0 else None})
+        out = {"architecture": "Pufevik", "vocab": self.vocab_size, "width": self.hidden_size,
+               "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps}, "layers": layers}
+        if self.bos_token_id >= 0:
+            out["bos_token_id"] = self.bos_token_id
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out

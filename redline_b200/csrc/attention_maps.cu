@@ -8,7 +8,11 @@
 //   key j is visible from i when    j <= i and (i - j < window or j < keep_first)      (window 0: all)
 //   a_{h,m} = softmax_j(s) V_g
 //   M = 1:  o_h = a_{h,0};          M = 2:  o_h = a_{h,0} - lambda * a_{h,1}
-//   unit_norm:  o_h <- o_h / sqrt(mean(o_h^2) + eps) * post_scale
+//   sink:       a learned number per head joins the softmax's denominator, exp(sink_h) once, with no key and
+//               no value (M = 1)
+//   unit_norm:  o_h <- o_h / sqrt(mean(o_h^2) + eps)
+//   o_h <- o_h * post_scale, and with a gate o_h <- o_h * sigmoid(gate), the gate one number per head
+//   (gate_mode 1: gate[token, h]) or per entry (gate_mode 2: gate[token, h * DV + d])
 //
 // Layouts: q [tokens, q_stride] with row (h, m) at column (h * M + m) * D; the key cache
 // [pages, G * M, page_size, D] (kv head g's map m is head g * M + m); the value cache
@@ -43,6 +47,20 @@ struct MaskArgs {
   int window, keep_first;
 };
 
+// What follows the softmax: a sink in the denominator, a gate on the output.
+template <typename T>
+struct TailArgs {
+  const float* sink;     // [heads] or null
+  const T* gate;         // rows of gate_stride entries, or null
+  int gate_stride, gate_mode;
+};
+template <typename T>
+__device__ __forceinline__ float gate_factor(const TailArgs<T>& t, size_t tok, int head, int d, int dv) {
+  if (t.gate_mode == 0) return 1.f;
+  const float g = to_float(t.gate[tok * t.gate_stride + (t.gate_mode == 1 ? head : head * dv + d)]);
+  return 1.f / (1.f + expf(-g));
+}
+
 __device__ __forceinline__ bool key_visible(int j, int i, const MaskArgs& mk) {
   return j <= i && (mk.window <= 0 || i - j < mk.window || j < mk.keep_first);
 }
@@ -76,6 +94,7 @@ struct MapsDecodeArgs {
   MaskArgs mask;
   float scale, softcap, lambda, post_scale, eps;
   int unit_norm;
+  TailArgs<T> tail;
 };
 
 // Lane l of the 8 that share a key takes elements l, l + 8, ... of the key in pieces of E elements.
@@ -278,8 +297,10 @@ maps_merge_kernel(const MapsDecodeArgs<T> a) {
     for (int p = 0; p <= p_hi; ++p)
       if (range_visible(p * kPart, min(ctx, (p + 1) * kPart), me, a.mask)) mx = fmaxf(mx, a.part_ml[(row0 + p) * 2]);
     const float coef = m == 0 ? 1.f : -a.lambda;
+    const bool sunk = kM == 1 && a.tail.sink != nullptr;
+    if (sunk) mx = fmaxf(mx, a.tail.sink[head]);
     for (int d = threadIdx.x; d < kDV; d += kThreads) {
-      float num = 0.f, den = 0.f;
+      float num = 0.f, den = sunk ? expf(a.tail.sink[head] - mx) : 0.f;
       for (int p = 0; p <= p_hi; ++p) {
         if (!range_visible(p * kPart, min(ctx, (p + 1) * kPart), me, a.mask)) continue;
         const float w = expf(a.part_ml[(row0 + p) * 2] - mx);
@@ -290,14 +311,15 @@ maps_merge_kernel(const MapsDecodeArgs<T> a) {
     }
   }
   __syncthreads();
-  float r = 1.f;
+  float r = a.post_scale;
   if (a.unit_norm) {
     float q = 0.f;
     for (int d = threadIdx.x; d < kDV; d += kThreads) q += o[d] * o[d];
-    r = rsqrtf(block_sum(q, scratch) / static_cast<float>(kDV) + a.eps) * a.post_scale;
+    r *= rsqrtf(block_sum(q, scratch) / static_cast<float>(kDV) + a.eps);
   }
   for (int d = threadIdx.x; d < kDV; d += kThreads)
-    a.out[static_cast<size_t>(tok) * a.out_stride + head * kDV + d] = from_float<T>(o[d] * r);
+    a.out[static_cast<size_t>(tok) * a.out_stride + head * kDV + d] =
+        from_float<T>(o[d] * r * gate_factor(a.tail, tok, head, d, kDV));
 }
 
 // ------------------------------------------------------------------ prompt portions
@@ -321,6 +343,7 @@ struct MapsPrefillArgs {
   MaskArgs mask;
   float scale, softcap, lambda, post_scale, eps;
   int unit_norm;
+  TailArgs<T> tail;
 };
 
 // Thread t owns query row r = t / 4 and the columns c = t % 4 + 4 i of every tile.
@@ -435,23 +458,33 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
         for (int i = 0; i < kDV / 4; ++i) acc[i] += p * Vs[c * kDV + cq + 4 * i];
       }
     }
+    if (kM == 1 && a.tail.sink != nullptr && mx != -INFINITY) {
+      // the sink joins the denominator; the reference maximum moves to it if it is the larger
+      const float sk = a.tail.sink[head];
+      const float m_new = fmaxf(mx, sk);
+      const float alpha = expf(mx - m_new);
+      l = l * alpha + expf(sk - m_new);
+#pragma unroll
+      for (int i = 0; i < kDV / 4; ++i) acc[i] *= alpha;
+    }
     const float coef = (m == 0 ? 1.f : -a.lambda) / (l > 0.f ? l : 1.f);
 #pragma unroll
     for (int i = 0; i < kDV / 4; ++i) o[i] += coef * acc[i];
   }
-  float scale_out = 1.f;
+  float scale_out = a.post_scale;
   if (a.unit_norm) {
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < kDV / 4; ++i) q += o[i] * o[i];
     q += __shfl_xor_sync(0xffffffffu, q, 1);
     q += __shfl_xor_sync(0xffffffffu, q, 2);
-    scale_out = rsqrtf(q / static_cast<float>(kDV) + a.eps) * a.post_scale;
+    scale_out *= rsqrtf(q / static_cast<float>(kDV) + a.eps);
   }
   if (r < rows) {
 #pragma unroll
     for (int i = 0; i < kDV / 4; ++i)
-      a.out[static_cast<size_t>(tok0 + r) * a.out_stride + head * kDV + cq + 4 * i] = from_float<T>(o[i] * scale_out);
+      a.out[static_cast<size_t>(tok0 + r) * a.out_stride + head * kDV + cq + 4 * i] =
+          from_float<T>(o[i] * scale_out * gate_factor(a.tail, tok0 + r, head, cq + 4 * i, kDV));
   }
 }
 
@@ -682,6 +715,21 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (kM == 1 && a.tail.sink != nullptr) {
+      // the sink joins the denominators; a row's reference maximum moves to it if it is the larger
+      const float sk = a.tail.sink[head];
+      const float n0 = fmaxf(mx0, sk), n1 = fmaxf(mx1, sk);
+      const float al0 = mx0 == -INFINITY ? 0.f : expf(mx0 - n0), al1 = mx1 == -INFINITY ? 0.f : expf(mx1 - n1);
+      l0 = l0 * al0 + expf(sk - n0);
+      l1 = l1 * al1 + expf(sk - n1);
+#pragma unroll
+      for (int nd = 0; nd < kDV / 8; ++nd) {
+        o[nd][0] *= al0;
+        o[nd][1] *= al0;
+        o[nd][2] *= al1;
+        o[nd][3] *= al1;
+      }
+    }
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
     if (kM == 2 && m == 0) {
       // (every thread reads back exactly what it wrote: no barrier is needed for O0)
@@ -714,7 +762,7 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
       }
     }
   }
-  float g0 = 1.f, g1 = 1.f;
+  float g0 = a.post_scale, g1 = a.post_scale;
   if (a.unit_norm) {
     float q0 = 0.f, q1 = 0.f;
 #pragma unroll
@@ -726,17 +774,25 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
     q0 += __shfl_xor_sync(0xffffffffu, q0, 2);
     q1 += __shfl_xor_sync(0xffffffffu, q1, 1);
     q1 += __shfl_xor_sync(0xffffffffu, q1, 2);
-    g0 = rsqrtf(q0 / static_cast<float>(kDV) + a.eps) * a.post_scale;
-    g1 = rsqrtf(q1 / static_cast<float>(kDV) + a.eps) * a.post_scale;
+    g0 *= rsqrtf(q0 / static_cast<float>(kDV) + a.eps);
+    g1 *= rsqrtf(q1 / static_cast<float>(kDV) + a.eps);
   }
+  if (a.tail.gate_mode == 1) {             // one gate per head: it joins the row's factor
+    if (ok0) g0 *= gate_factor(a.tail, tok0 + r0, head, 0, kDV);
+    if (ok1) g1 *= gate_factor(a.tail, tok0 + r1, head, 0, kDV);
+  }
+  const bool each = a.tail.gate_mode == 2;
 #pragma unroll
   for (int nd = 0; nd < kDV / 8; ++nd) {
+    const int d = nd * 8 + tig * 2;
     if (ok0)
-      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok0 + r0) * a.out_stride + head * kDV + nd * 8 + tig * 2) =
-          __floats2bfloat162_rn(o[nd][0] * g0, o[nd][1] * g0);
+      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok0 + r0) * a.out_stride + head * kDV + d) =
+          __floats2bfloat162_rn(o[nd][0] * g0 * (each ? gate_factor(a.tail, tok0 + r0, head, d, kDV) : 1.f),
+                                o[nd][1] * g0 * (each ? gate_factor(a.tail, tok0 + r0, head, d + 1, kDV) : 1.f));
     if (ok1)
-      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok0 + r1) * a.out_stride + head * kDV + nd * 8 + tig * 2) =
-          __floats2bfloat162_rn(o[nd][2] * g1, o[nd][3] * g1);
+      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok0 + r1) * a.out_stride + head * kDV + d) =
+          __floats2bfloat162_rn(o[nd][2] * g1 * (each ? gate_factor(a.tail, tok0 + r1, head, d, kDV) : 1.f),
+                                o[nd][3] * g1 * (each ? gate_factor(a.tail, tok0 + r1, head, d + 1, kDV) : 1.f));
   }
 }
 #endif  // sizes that are multiples of 16
@@ -752,8 +808,13 @@ template <typename T>
 int launch_maps_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt, int max_blocks,
                        const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out, int out_stride,
                        int nitems, int heads, int kv_heads, int page_size, int window, int keep_first, float scale,
-                       float softcap, float lambda, float post_scale, float eps, int unit_norm, cudaStream_t stream) {
+                       float softcap, float lambda, float post_scale, float eps, int unit_norm, const float* sink,
+                       const void* gate, int gate_stride, int gate_mode, cudaStream_t stream) {
   MapsDecodeArgs<T> a;
+  a.tail.sink = sink;
+  a.tail.gate = static_cast<const T*>(gate);
+  a.tail.gate_stride = gate_stride;
+  a.tail.gate_mode = gate == nullptr ? 0 : gate_mode;
   a.q = static_cast<const T*>(q);
   a.q_stride = q_stride;
   a.kcache = static_cast<const T*>(kc);
@@ -788,8 +849,13 @@ int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void*
                         const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
                         const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
                         int kv_heads, int page_size, int window, int keep_first, float scale, float softcap,
-                        float lambda, float post_scale, float eps, int unit_norm, int impl, cudaStream_t stream) {
+                        float lambda, float post_scale, float eps, int unit_norm, const float* sink, const void* gate,
+                        int gate_stride, int gate_mode, int impl, cudaStream_t stream) {
   MapsPrefillArgs<T> a;
+  a.tail.sink = sink;
+  a.tail.gate = static_cast<const T*>(gate);
+  a.tail.gate_stride = gate_stride;
+  a.tail.gate_mode = gate == nullptr ? 0 : gate_mode;
   a.q = static_cast<const T*>(q);
   a.q_stride = q_stride;
   a.kcache = static_cast<const T*>(kc);
@@ -854,30 +920,33 @@ int rl_maps_decode(int dtype, const void* q, int q_stride, const void* kc, const
                    int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out,
                    int out_stride, int nitems, int heads, int kv_heads, int page_size, int window, int keep_first,
                    float scale, float softcap, float lambda, float post_scale, float eps, int unit_norm,
-                   cudaStream_t stream) {
+                   const float* sink, const void* gate, int gate_stride, int gate_mode, cudaStream_t stream) {
   if (nitems <= 0 || max_parts <= 0) return 0;
   if (dtype == 0)
     return launch_maps_decode<float>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, out,
                                      out_stride, nitems, heads, kv_heads, page_size, window, keep_first, scale, softcap,
-                                     lambda, post_scale, eps, unit_norm, stream);
+                                     lambda, post_scale, eps, unit_norm, sink, gate, gate_stride, gate_mode, stream);
   return launch_maps_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, out,
                                   out_stride, nitems, heads, kv_heads, page_size, window, keep_first, scale, softcap,
-                                  lambda, post_scale, eps, unit_norm, stream);
+                                  lambda, post_scale, eps, unit_norm, sink, gate, gate_stride, gate_mode, stream);
 }
 
 int rl_maps_prefill(int dtype, const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                     int max_blocks, const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
                     const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
                     int kv_heads, int page_size, int window, int keep_first, float scale, float softcap, float lambda,
-                    float post_scale, float eps, int unit_norm, int impl, cudaStream_t stream) {
+                    float post_scale, float eps, int unit_norm, const float* sink, const void* gate, int gate_stride,
+                    int gate_mode, int impl, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (dtype == 0)
     return launch_maps_prefill<float>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
                                       out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
-                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, impl, stream);
+                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, sink, gate, gate_stride,
+                                      gate_mode, impl, stream);
   return launch_maps_prefill<bf16>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
                                    out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
-                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, impl, stream);
+                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, sink, gate, gate_stride,
+                                      gate_mode, impl, stream);
 }
 
 }  // extern "C"

@@ -24,11 +24,11 @@ __global__ void resolve_ids_kernel(int32_t* __restrict__ ids, const int32_t* __r
 }
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = float(table[ids[t], :]); `out` is the float residual stream.
+// out[t, :] = float(table[ids[t], :]) * scale; `out` is the float residual stream.
 // A token id outside [0, vocab) sets bit 0 of *status and yields a zero row.
 template <typename TW>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ table,
-                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
@@ -40,7 +40,7 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const TW* __re
     return;
   }
   const TW* row = table + static_cast<size_t>(id) * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = to_float(row[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = to_float(row[c]) * scale;
 }
 
 // ------------------------------------------------------- add + RMSNorm
@@ -328,15 +328,15 @@ int rl_resolve_ids(int32_t* ids, const int32_t* src, const int32_t* sampled, int
 }
 
 int rl_embedding(const int32_t* ids, const void* table, int table_dtype, float* out, int tokens,
-                 int hidden, int vocab, int* status, cudaStream_t stream) {
+                 int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int th = row_threads(hidden);
   if (table_dtype == RL_F32) {
     launch_kernel(embedding_kernel<float>, dim3(tokens), dim3(th), 0, stream, ids, static_cast<const float*>(table), out,
-                                                       hidden, vocab, status);
+                                                       hidden, vocab, scale, status);
   } else {
     launch_kernel(embedding_kernel<bf16>, dim3(tokens), dim3(th), 0, stream, ids, static_cast<const bf16*>(table), out,
-                                                      hidden, vocab, status);
+                                                      hidden, vocab, scale, status);
   }
   RL_LAUNCH_END();
 }

@@ -1,0 +1,267 @@
+// A matrix memory per head with exponential gates and a running stabiliser (the mLSTM cell), as a
+// recurrence over a state kept per request:
+//
+//   m_t = max(f_t + m_(t-1), i_t)                       i_t, f_t: logarithms of the input and forget gates
+//   a_t = exp(f_t + m_(t-1) - m_t),  b_t = exp(i_t - m_t)
+//   S_t = a_t S_(t-1) + b_t k_t v_t^T                   S is [D, DV] per head
+//   n_t = a_t n_(t-1) + b_t k_t                         n is [D]
+//   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + floor)
+//
+// with S = 0, n = 0 and m = 0 at the start of a sequence.  n is kept as one more column of S (the
+// column of a value that is always 1), so that one thread per column serves both; a request's state
+// is [heads, D, DV + 1] floats followed by [heads] stabilisers.
+//
+// Three kernels.  (1) gates: the gate projections (float32, [tokens, 2 heads]: input gates, then forget
+// gates) get their bias, the cap c tanh(z / c) and, the forget gate, the logarithm of the sigmoid; the
+// stabiliser is carried along the sequence's tokens; a_t, b_t replace the projections and m_t goes to a
+// buffer of its own.  (2) recurrence: a CTA takes one sequence, one head and a block of columns; thread j
+// keeps column j of the state (D floats) in registers, from the request's slot and back.  It writes the
+// numerators S^T q (float32) and, from the extra column, n . q.  (3) output: the division, every head's
+// unit-RMS norm, the weight, the sigmoid gate and a constant factor, into the activation type.
+//
+// A sequence's tokens are contiguous and in order in a step; CTAs find them by searching the step's
+// token -> sequence map.  Gates, stabiliser, state, sums and norms are float32; q, k and v are read from
+// the projection buffer in the activation type.
+#include "common.cuh"
+
+#ifndef RL_MM_DIM
+#error "compile with -DRL_MM_DIM=<key size>"
+#endif
+
+namespace rl {
+
+constexpr int kD = RL_MM_DIM;
+static_assert(kD >= 1 && kD <= 256, "key size out of range");
+constexpr int kTok = 16;          // tokens staged in shared memory at a time
+constexpr int kGateThreads = 128;
+
+// First token index t in [0, n) with seq_of_token[t] >= s.
+__device__ __forceinline__ int first_token_of(const int32_t* __restrict__ seq_of_token, int n, int s) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (seq_of_token[mid] < s) lo = mid + 1;
+    else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float capped(float z, float cap) { return cap > 0.f ? cap * tanhf(z / cap) : z; }
+
+struct MemoryLayout {
+  int heads, dv;
+  __host__ __device__ size_t plane() const { return static_cast<size_t>(kD) * (dv + 1); }
+  __host__ __device__ size_t slot_floats() const { return heads * plane() + heads; }
+};
+
+// ---------------------------------------------------------------- (1) gates and stabiliser
+// gates [tokens, 2 heads] float32 in place: (z_i, z_f) -> (b_t, a_t); stab [tokens, heads] <- m_t.
+__global__ void __launch_bounds__(kGateThreads)
+memory_gates_kernel(float* __restrict__ gates, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
+                    float cap, const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ state_slot,
+                    float* __restrict__ state, float* __restrict__ stab, int tokens, MemoryLayout lay) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float si[kGateThreads], sf[kGateThreads], sm[kGateThreads + 1];
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const int t_begin = first_token_of(seq_of_token, tokens, seq);
+  const int t_end = first_token_of(seq_of_token, tokens, seq + 1);
+  if (t_begin >= t_end) return;
+  float* m_state = state + static_cast<size_t>(state_slot[seq]) * lay.slot_floats() + lay.heads * lay.plane() + head;
+  const float bi = bias_i != nullptr ? bias_i[head] : 0.f, bf = bias_f != nullptr ? bias_f[head] : 0.f;
+  if (threadIdx.x == 0) sm[0] = *m_state;
+  for (int t0 = t_begin; t0 < t_end; t0 += kGateThreads) {
+    const int n = min(kGateThreads, t_end - t0);
+    const int t = t0 + threadIdx.x;
+    float gi = 0.f, gf = 0.f;
+    if (threadIdx.x < n) {
+      float* row = gates + static_cast<size_t>(t) * (2 * lay.heads);
+      gi = capped(row[head] + bi, cap);
+      gf = log_sigmoid(capped(row[lay.heads + head] + bf, cap));
+      si[threadIdx.x] = gi;
+      sf[threadIdx.x] = gf;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {           // the stabiliser along the tokens; sm[j + 1] is m after token j
+      float m = sm[0];
+      for (int j = 0; j < n; ++j) {
+        m = fmaxf(sf[j] + m, si[j]);
+        sm[j + 1] = m;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < n) {
+      const float m_prev = sm[threadIdx.x], m_new = sm[threadIdx.x + 1];
+      float* row = gates + static_cast<size_t>(t) * (2 * lay.heads);
+      row[head] = expf(gi - m_new);
+      row[lay.heads + head] = expf(gf + m_prev - m_new);
+      stab[static_cast<size_t>(t) * lay.heads + head] = m_new;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) sm[0] = sm[n];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *m_state = sm[0];
+}
+
+// ---------------------------------------------------------------- (2) the recurrence
+template <typename T>
+struct MemoryArgs {
+  const T* qkv;           // [tokens, ld]: q at q_col + h * D, k at k_col + h * D, v at v_col + h * DV
+  int ld, q_col, k_col, v_col;
+  float q_scale;
+  const float* gates;     // [tokens, 2 heads]: b_t, then a_t
+  const int32_t* seq_of_token;
+  const int32_t* state_slot;
+  float* state;           // [slots] x ([heads, D, DV + 1] + [heads])
+  float* num;             // [tokens, heads * DV]: S^T q
+  float* qn;              // [tokens, heads]: n . q
+  int tokens;
+  MemoryLayout lay;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+memory_recurrence_kernel(const MemoryArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float qs[kTok][kD];
+  __shared__ float ks[kTok][kD];       // b_t k_t
+  __shared__ float as[kTok];
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int dv = a.lay.dv;
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool mine = col <= dv;         // column dv is n
+  const int t_begin = first_token_of(a.seq_of_token, a.tokens, seq);
+  const int t_end = first_token_of(a.seq_of_token, a.tokens, seq + 1);
+  if (t_begin >= t_end) return;
+  float* plane = a.state + static_cast<size_t>(a.state_slot[seq]) * a.lay.slot_floats() + head * a.lay.plane();
+  float S[kD];
+#pragma unroll
+  for (int i = 0; i < kD; ++i) S[i] = mine ? plane[static_cast<size_t>(i) * (dv + 1) + col] : 0.f;
+
+  for (int tb = t_begin; tb < t_end; tb += kTok) {
+    const int nt = min(kTok, t_end - tb);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * kD; i += blockDim.x) {
+      const int tt = i / kD, d = i - tt * kD;
+      const T* row = a.qkv + static_cast<size_t>(tb + tt) * a.ld;
+      const float b = a.gates[static_cast<size_t>(tb + tt) * (2 * a.lay.heads) + head];
+      qs[tt][d] = to_float(row[a.q_col + head * kD + d]) * a.q_scale;
+      ks[tt][d] = to_float(row[a.k_col + head * kD + d]) * b;
+    }
+    for (int tt = threadIdx.x; tt < nt; tt += blockDim.x)
+      as[tt] = a.gates[static_cast<size_t>(tb + tt) * (2 * a.lay.heads) + a.lay.heads + head];
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      float v = 0.f;
+      if (col < dv) v = to_float(a.qkv[static_cast<size_t>(tb + tt) * a.ld + a.v_col + head * dv + col]);
+      else if (col == dv) v = 1.f;
+      const float decay = as[tt];
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < kD; ++i) {
+        S[i] = fmaf(decay, S[i], ks[tt][i] * v);
+        o = fmaf(S[i], qs[tt][i], o);
+      }
+      if (col < dv) a.num[static_cast<size_t>(tb + tt) * (a.lay.heads * dv) + head * dv + col] = o;
+      else if (col == dv) a.qn[static_cast<size_t>(tb + tt) * a.lay.heads + head] = o;
+    }
+  }
+  if (!mine) return;
+#pragma unroll
+  for (int i = 0; i < kD; ++i) plane[static_cast<size_t>(i) * (dv + 1) + col] = S[i];
+}
+
+// ---------------------------------------------------------------- (3) division, unit norm, weight, gate
+// One CTA per token, a warp per head in turn.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128)
+memory_output_kernel(const float* __restrict__ num, const float* __restrict__ qn, const float* __restrict__ stab,
+                     const TA* __restrict__ gate, int ld_gate, const TW* __restrict__ w, TA* __restrict__ out,
+                     int ld_out, int heads, int dv, float eps, float floor, float out_scale) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < heads; h += nwarps) {
+    const float den = fmaxf(fabsf(qn[static_cast<size_t>(t) * heads + h]), expf(-stab[static_cast<size_t>(t) * heads + h])) + floor;
+    const float* o = num + static_cast<size_t>(t) * heads * dv + h * dv;
+    float q = 0.f;
+    for (int d = lane; d < dv; d += 32) {
+      const float v = o[d] / den;
+      q += v * v;
+    }
+    const float r = rsqrtf(warp_sum(q) / static_cast<float>(dv) + eps);
+    for (int d = lane; d < dv; d += 32) {
+      const int c = h * dv + d;
+      float y = o[d] / den * r * to_float(w[c]) * out_scale;
+      if (gate != nullptr) y *= 1.f / (1.f + expf(-to_float(gate[static_cast<size_t>(t) * ld_gate + c])));
+      out[static_cast<size_t>(t) * ld_out + c] = from_float<TA>(y);
+    }
+  }
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+extern "C" {
+
+enum { RL_F32 = 0, RL_BF16 = 1 };
+
+// Floats of one request's state for `heads` heads with values of `dv` entries.
+long long rl_memory_state_floats(int heads, int dv) {
+  MemoryLayout lay{heads, dv};
+  return static_cast<long long>(lay.slot_floats());
+}
+
+int rl_memory_gates(float* gates, const float* bias_i, const float* bias_f, float cap, const int32_t* seq_of_token,
+                    const int32_t* state_slot, float* state, float* stab, int tokens, int sequences, int heads, int dv,
+                    cudaStream_t stream) {
+  if (tokens <= 0 || sequences <= 0) return 0;
+  MemoryLayout lay{heads, dv};
+  launch_kernel(memory_gates_kernel, dim3(heads, sequences), dim3(kGateThreads), 0, stream, gates, bias_i, bias_f, cap,
+                seq_of_token, state_slot, state, stab, tokens, lay);
+  RL_LAUNCH_END();
+}
+
+int rl_memory_recurrence(int dtype, const void* qkv, int ld, int q_col, int k_col, int v_col, float q_scale,
+                         const float* gates, const int32_t* seq_of_token, const int32_t* state_slot, float* state,
+                         float* num, float* qn, int tokens, int sequences, int heads, int dv, cudaStream_t stream) {
+  if (tokens <= 0 || sequences <= 0) return 0;
+  const int cols = dv + 1;
+  const int th = cols >= 128 ? 128 : (cols + 31) / 32 * 32;
+  const dim3 grid((cols + th - 1) / th, heads, sequences);
+#define RL_CASE(T)                                                                                  \
+  do {                                                                                              \
+    MemoryArgs<T> a;                                                                                \
+    a.qkv = static_cast<const T*>(qkv);                                                             \
+    a.ld = ld; a.q_col = q_col; a.k_col = k_col; a.v_col = v_col; a.q_scale = q_scale;              \
+    a.gates = gates; a.seq_of_token = seq_of_token; a.state_slot = state_slot; a.state = state;     \
+    a.num = num; a.qn = qn; a.tokens = tokens; a.lay = MemoryLayout{heads, dv};                     \
+    launch_kernel(memory_recurrence_kernel<T>, grid, dim3(th), 0, stream, a);                       \
+  } while (0)
+  if (dtype == RL_F32) RL_CASE(float);
+  else RL_CASE(bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_memory_output(const float* num, const float* qn, const float* stab, const void* gate, int ld_gate,
+                     const void* w, int w_dtype, void* out, int ld_out, int act_dtype, int tokens, int heads, int dv,
+                     float eps, float floor, float out_scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+#define RL_CASE(TA, TW)                                                                                          \
+  launch_kernel(memory_output_kernel<TA, TW>, dim3(tokens), dim3(128), 0, stream, num, qn, stab,                \
+                static_cast<const TA*>(gate), ld_gate, static_cast<const TW*>(w), static_cast<TA*>(out), ld_out, \
+                heads, dv, eps, floor, out_scale)
+  if (act_dtype == RL_F32) RL_CASE(float, float);
+  else if (w_dtype == RL_F32) RL_CASE(bf16, float);
+  else RL_CASE(bf16, bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+}  // extern "C"

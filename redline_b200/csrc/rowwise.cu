@@ -1,7 +1,10 @@
 // Row-wise kernels for blocks that norm a sublayer's input AND its output: layer norm (weight, no
 // bias) fused with the add to the float32 residual stream and with the norm that follows; bias +
-// activation over a range of columns; the write of any per-token tensor into its paged cache; and
-// the gated unit-RMS norm that closes a linear-attention mixer.
+// activation over a range of columns; the write of any per-token tensor into its paged cache; the
+// gated unit-RMS norm that closes a linear-attention mixer; a gated activation act(gate) * up; and what
+// attention heads may need between their projection and the cache: an RMS norm of queries and keys
+// (per head or over the whole projection), a rotation of neighbouring pairs, a mix of the values with
+// those of an earlier layer.
 //
 // Activations are float or bfloat16; means, variances, the stream and the activations'
 // arithmetic are float.  The variance is the mean of squared deviations (two passes over a row
@@ -28,6 +31,8 @@ __device__ __forceinline__ float activate(float z, int mode) {
 //   delta / post_w given:  the sublayer's output is normed and added to the stream (written back)
 //   delta without post_w:  the sublayer's output is added as it is
 //   out / pre_w given:     the (new) stream row is normed for the next sublayer
+//   out without pre_w:     the (new) stream row is handed on as it is, in the activation type (blocks
+//                          whose sublayers read the stream itself)
 //   rows_idx given:        out row i comes from stream row rows_idx[i]; nothing is added (delta is null)
 // kind: 0 layer norm (mean removed), 1 RMS norm; both with a weight and without a bias.
 template <typename TA, typename TW>
@@ -74,6 +79,11 @@ __global__ void sandwich_norm_kernel(float* __restrict__ residual, const TA* __r
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) row[c] = res[c];
   }
   if (out == nullptr) return;
+  if (pre_w == nullptr) {
+    TA* o = out + static_cast<size_t>(r) * ld_out;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_float<TA>(row[c]);
+    return;
+  }
   float s = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) s += row[c];
   const float mean = kind == 0 ? block_sum(s, scratch) * inv_n : 0.f;
@@ -111,7 +121,7 @@ __global__ void sandwich_norm_reg_kernel(float* __restrict__ residual, const TA*
     v[i] = in ? res[c] : 0.f;
     d[i] = (in && delta != nullptr) ? to_float(delta[static_cast<size_t>(src) * ld_delta + c]) : 0.f;
     pw[i] = (in && post_w != nullptr) ? to_float(post_w[c]) : 0.f;
-    nw[i] = (in && out != nullptr) ? to_float(pre_w[c]) : 0.f;
+    nw[i] = (in && out != nullptr && pre_w != nullptr) ? to_float(pre_w[c]) : 0.f;
   }
   if (delta != nullptr) {
     if (post_w == nullptr) {
@@ -139,6 +149,15 @@ __global__ void sandwich_norm_reg_kernel(float* __restrict__ residual, const TA*
     }
   }
   if (out == nullptr) return;
+  if (pre_w == nullptr) {
+    TA* o = out + static_cast<size_t>(r) * ld_out;
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < hidden) o[c] = from_float<TA>(v[i]);
+    }
+    return;
+  }
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < EPT; ++i) s += v[i];
@@ -230,7 +249,113 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const TA* __re
   }
 }
 
+// ------------------------------------------------ out[r, i] = act(gu[r, i]) * gu[r, inter + i]
+template <typename TA>
+__global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restrict__ out, int inter, int mode) {
+  pdl_launch();
+  pdl_wait();
+  const TA* g = gu + static_cast<size_t>(blockIdx.y) * ld;
+  TA* o = out + static_cast<size_t>(blockIdx.y) * inter;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < inter; c += gridDim.x * blockDim.x)
+    o[c] = from_float<TA>(activate(to_float(g[c]), mode) * to_float(g[inter + c]));
+}
+
+// ------------------------------------------------ queries, keys and values between projection and cache
+// In place on the rows of a projection buffer, one CTA per token.  Two sections of heads (queries at
+// q_col, keys at k_col; `dim` entries a head) are, in float32,
+//   normed:   x / sqrt(mean(x^2) + eps) * w, the mean over one head (norm_mode 1, w of `dim` entries for all
+//             heads) or over the whole section (norm_mode 2, w of heads * dim entries); 0: not normed;
+//   rotated:  entries (2i, 2i+1), i < rot_pairs, of every head turn by the angle whose cosine and sine are
+//             cos[pos, i] and sin[pos, i] (tables [max_pos, rot_pairs]); the other entries stay.
+// The values (v_size entries at v_col) are, with vmix_mode 1, copied to v_first [tokens, v_size]; with
+// vmix_mode 2 replaced by (1 - lam) v + lam v_first.  A position beyond the tables sets bit 1 of *status.
+struct HeadPrepArgs {
+  int ld, q_col, q_heads, k_col, k_heads, dim, norm_mode;
+  float eps;
+  int rot_pairs, max_pos, v_col, v_size, vmix_mode;
+  float lam;
+};
+
+template <typename TA, typename TW>
+__global__ void head_prep_kernel(TA* __restrict__ x, const int32_t* __restrict__ positions,
+                                 const TW* __restrict__ q_w, const TW* __restrict__ k_w,
+                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                 TA* __restrict__ v_first, int* status, const HeadPrepArgs a) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float head_sq[];           // per head of the section: sum of squares, then the factor
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  TA* row = x + static_cast<size_t>(t) * a.ld;
+  int pos = positions[t];
+  if (a.rot_pairs > 0 && (pos < 0 || pos >= a.max_pos)) {
+    if (threadIdx.x == 0) atomicOr(status, 2);
+    pos = 0;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int sec = 0; sec < 2; ++sec) {
+    const int heads = sec == 0 ? a.q_heads : a.k_heads;
+    TA* p = row + (sec == 0 ? a.q_col : a.k_col);
+    const TW* w = sec == 0 ? q_w : k_w;
+    if (heads <= 0) continue;
+    __syncthreads();
+    if (a.norm_mode != 0) {
+      for (int h = warp; h < heads; h += nwarps) {
+        float q = 0.f;
+        for (int d = lane; d < a.dim; d += 32) {
+          const float v = to_float(p[h * a.dim + d]);
+          q += v * v;
+        }
+        q = warp_sum(q);
+        if (lane == 0) head_sq[h] = q;
+      }
+      __syncthreads();
+      if (a.norm_mode == 2) {
+        float q = 0.f;
+        for (int h = threadIdx.x; h < heads; h += blockDim.x) q += head_sq[h];
+        q = block_sum(q, scratch);
+        __syncthreads();
+        const float r = rsqrtf(q / static_cast<float>(heads * a.dim) + a.eps);
+        for (int h = threadIdx.x; h < heads; h += blockDim.x) head_sq[h] = r;
+      } else {
+        for (int h = threadIdx.x; h < heads; h += blockDim.x)
+          head_sq[h] = rsqrtf(head_sq[h] / static_cast<float>(a.dim) + a.eps);
+      }
+      __syncthreads();
+    }
+    const int n = heads * a.dim;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int h = i / a.dim, d = i - h * a.dim;
+      const bool paired = d < 2 * a.rot_pairs;
+      if (paired && (d & 1)) continue;            // the odd entry of a pair goes with the even one
+      const float r = a.norm_mode != 0 ? head_sq[h] : 1.f;
+      const int wi = a.norm_mode == 2 ? i : d;
+      float u = to_float(p[i]) * r;
+      if (a.norm_mode != 0) u *= to_float(w[wi]);
+      if (!paired) {
+        if (a.norm_mode != 0) p[i] = from_float<TA>(u);
+        continue;
+      }
+      float v = to_float(p[i + 1]) * r;
+      if (a.norm_mode != 0) v *= to_float(w[wi + 1]);
+      const float c = cos_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+      const float s = sin_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+      p[i] = from_float<TA>(u * c - v * s);
+      p[i + 1] = from_float<TA>(v * c + u * s);
+    }
+  }
+  if (a.vmix_mode != 0) {
+    TA* v = row + a.v_col;
+    TA* f = v_first + static_cast<size_t>(t) * a.v_size;
+    for (int i = threadIdx.x; i < a.v_size; i += blockDim.x) {
+      if (a.vmix_mode == 1) f[i] = v[i];
+      else v[i] = from_float<TA>((1.f - a.lam) * to_float(v[i]) + a.lam * to_float(f[i]));
+    }
+  }
+}
+
 }  // namespace rl
+
 
 using namespace rl;
 
@@ -306,6 +431,43 @@ int rl_gated_rmsnorm(const float* o, const void* gate, int ld_gate, const void* 
 #define RL_CASE(TA, TW)                                                                                        \
   launch_kernel(gated_rmsnorm_kernel<TA, TW>, dim3(rows), dim3(th), 0, stream, o, static_cast<const TA*>(gate), \
                 ld_gate, static_cast<const TW*>(w), static_cast<TA*>(out), n, eps)
+  if (act_dtype == RL_F32) RL_CASE(float, float);
+  else if (w_dtype == RL_F32) RL_CASE(bf16, float);
+  else RL_CASE(bf16, bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_gated_act(const void* gu, int ld, void* out, int act_dtype, int rows, int inter, int mode,
+                 cudaStream_t stream) {
+  if (rows <= 0 || inter <= 0) return 0;
+  const int th = 256;
+  dim3 grid(min((inter + th - 1) / th, 64), rows);
+  if (act_dtype == RL_F32)
+    launch_kernel(gated_act_kernel<float>, grid, dim3(th), 0, stream, static_cast<const float*>(gu), ld,
+                  static_cast<float*>(out), inter, mode);
+  else
+    launch_kernel(gated_act_kernel<bf16>, grid, dim3(th), 0, stream, static_cast<const bf16*>(gu), ld,
+                  static_cast<bf16*>(out), inter, mode);
+  RL_LAUNCH_END();
+}
+
+int rl_head_prep(void* x, int act_dtype, int ld, const int32_t* positions, int tokens, int q_col, int q_heads,
+                 int k_col, int k_heads, int dim, const void* q_w, const void* k_w, int w_dtype, int norm_mode,
+                 float eps, const float* cos_t, const float* sin_t, int rot_pairs, int max_pos, int v_col,
+                 int v_size, void* v_first, int vmix_mode, float lam, int* status, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  HeadPrepArgs a;
+  a.ld = ld; a.q_col = q_col; a.q_heads = q_heads; a.k_col = k_col; a.k_heads = k_heads; a.dim = dim;
+  a.norm_mode = norm_mode; a.eps = eps; a.rot_pairs = rot_pairs; a.max_pos = max_pos; a.v_col = v_col;
+  a.v_size = v_size; a.vmix_mode = vmix_mode; a.lam = lam;
+  const int widest = max(q_heads, k_heads) * dim;
+  const int th = widest >= 1024 ? 512 : (widest >= 256 ? 256 : 128);
+  const size_t smem = static_cast<size_t>(max(max(q_heads, k_heads), 1)) * sizeof(float);
+#define RL_CASE(TA, TW)                                                                                          \
+  launch_kernel(head_prep_kernel<TA, TW>, dim3(tokens), dim3(th), smem, stream, static_cast<TA*>(x), positions, \
+                static_cast<const TW*>(q_w), static_cast<const TW*>(k_w), cos_t, sin_t,                          \
+                static_cast<TA*>(v_first), status, a)
   if (act_dtype == RL_F32) RL_CASE(float, float);
   else if (w_dtype == RL_F32) RL_CASE(bf16, float);
   else RL_CASE(bf16, bf16);

@@ -153,8 +153,9 @@ class StepContext:
     hand_in: Optional[object] = None           # what the part before left for the running part's norm
     hand_out: Optional[object] = None          # what the running part leaves
     block_next_norm: Optional[object] = None   # set by the model: the first norm of the block after this one
+    block_next: Optional[object] = None        # set by the model: the block after this one (None after the last)
     block_hand: Optional[object] = None        # carried from a block's last part to the next block
-    block_normed: Optional[object] = None      # (norm, rows): a block's last kernel has already applied the next block's first norm
+    block_normed: Optional[object] = None      # (norm or mark, rows): a block's last kernel has already made the next block's first input
 
 
 @dataclass

@@ -26,9 +26,13 @@ class DecoderModel:
         self.blocks: List[Block] = []
         for ls in spec.layers:
             block_cls = lookup("block", ls.arrangement)
-            if (ls.ffn is None) != (ls.ffn_norm is None):
-                raise ValueError("a layer has a feed-forward and its norm, or neither")
-            self.blocks.append(block_cls(build_part("norm", ls.mixer_norm, rt), build_part("mixer", ls.mixer, rt),
+            reads_stream = getattr(block_cls, "reads_stream", False)     # its sublayers take the stream as it is
+            if reads_stream and (ls.mixer_norm is not None or ls.ffn_norm is not None or ls.mixer_post_norm is None):
+                raise ValueError(f"the block arrangement '{ls.arrangement}' norms its sublayers' outputs only")
+            if not reads_stream and (ls.mixer_norm is None or (ls.ffn is None) != (ls.ffn_norm is None)):
+                raise ValueError("a layer has a mixer with its norm, and a feed-forward with its norm or neither")
+            self.blocks.append(block_cls(build_part("norm", ls.mixer_norm, rt) if ls.mixer_norm is not None else None,
+                                         build_part("mixer", ls.mixer, rt),
                                          build_part("norm", ls.ffn_norm, rt) if ls.ffn_norm is not None else None,
                                          build_part("ffn", ls.ffn, rt) if ls.ffn is not None else None, rt))
             if ls.mixer_post_norm is not None or ls.ffn_post_norm is not None:
@@ -156,13 +160,14 @@ class DecoderModel:
         ctx.block_hand = ctx.block_normed = None
         for i, call in enumerate(order):
             # (the block after this one may take over its first norm from this block's last kernel)
-            ctx.block_next_norm = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) else None
+            ctx.block_next = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            ctx.block_next_norm = ctx.block_next.first_norm() if ctx.block_next is not None else None
             if self.nvtx_layers:
                 torch.cuda.nvtx.range_push(f"layer call {i} (layer {call.layer})")
             pending = self.blocks[call.layer].forward(residual, pending, ctx, caches[i], states[i])
             if self.nvtx_layers:
                 torch.cuda.nvtx.range_pop()
-        ctx.block_hand = ctx.block_next_norm = ctx.block_normed = None
+        ctx.block_hand = ctx.block_next_norm = ctx.block_normed = ctx.block_next = None
         head_w = getattr(self.head, "weight", None)
         if R > 0 and pending is None and self.head.forward_from(residual, self.final_norm, ctx.logit_rows, R, logits):
             op_mark(ctx, "final_norm+lm_head", head_w, R, nbytes=R * logits.shape[1] * 2.0)

@@ -88,12 +88,14 @@ def resolve_ids(ids: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor, n: 
     _check(f(_ptr(ids), _ptr(src), _ptr(sampled), n, _stream()), "resolve_ids")
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t] = float(table[ids[t]]); out is the float32 residual stream [T, H]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """out[t] = float(table[ids[t]]) * scale; out is the float32 residual stream [T, H]."""
     _need_cuda(ids, table, out)
-    f = _fn(_ew(), "rl_embedding", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    f = _fn(_ew(), "rl_embedding", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                                     c_void_p])
     _check(f(_ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), ids.numel(), table.shape[1],
-             table.shape[0], _ptr(status), _stream()), "embedding")
+             table.shape[0], float(scale), _ptr(status), _stream()), "embedding")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -579,8 +581,9 @@ def sandwich_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_w:
                   rows_idx: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
     """residual (float32 stream) += norm(delta) * post_w (delta given; without post_w delta is added as it
     is), then out = norm(residual) * pre_w (out given).  ``kind``: layer norm (mean removed, variance as the
-    mean of squared deviations) or RMS norm, both with a weight and no bias.  With ``rows_idx`` out row i
-    comes from stream row rows_idx[i] and nothing is added."""
+    mean of squared deviations) or RMS norm, both with a weight and no bias.  ``out`` without ``pre_w``
+    receives the (new) stream rows as they are, in its own type.  With ``rows_idx`` out row i comes from
+    stream row rows_idx[i] and nothing is added."""
     _need_cuda(residual, delta, out)
     n = rows if rows is not None else (rows_idx.numel() if rows_idx is not None else residual.shape[0])
     if residual.dtype != torch.float32 or not residual.is_contiguous():
@@ -591,8 +594,8 @@ def sandwich_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_w:
     if act is None:
         return
     ws = [w for w in (post_w, pre_w) if w is not None]
-    if (out is not None and pre_w is None) or any(w.dtype != ws[0].dtype for w in ws):
-        raise KernelError("sandwich_norm: an output needs its weight, and the weights one type")
+    if any(w.dtype != ws[0].dtype for w in ws):
+        raise KernelError("sandwich_norm: the weights must have one type")
     if delta is not None and out is not None and delta.dtype != out.dtype:
         raise KernelError("sandwich_norm: delta and out must have the same dtype")
     f = _fn(_rw(), "rl_sandwich_norm", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
@@ -643,6 +646,57 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out
              rows if rows is not None else o.shape[0], o.shape[1], float(eps), _stream()), "gated_rmsnorm")
 
 
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> None:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i], I = out.shape[1]."""
+    _need_cuda(gate_up, out)
+    if gate_up.stride(1) != 1 or not out.is_contiguous() or gate_up.dtype != out.dtype \
+            or gate_up.shape[1] != 2 * out.shape[1]:
+        raise KernelError("gated_act: [gate | up] rows of the output's type and twice its width")
+    f = _fn(_rw(), "rl_gated_act", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out.dtype), out.shape[0], out.shape[1], act,
+             _stream()), "gated_act")
+
+
+HEAD_NORM_NONE, HEAD_NORM_EACH, HEAD_NORM_WHOLE = 0, 1, 2
+VALUE_MIX_NONE, VALUE_MIX_KEEP, VALUE_MIX_BLEND = 0, 1, 2
+
+
+def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int, q_heads: int, k_col: int,
+              k_heads: int, dim: int, status: torch.Tensor, q_weight: Optional[torch.Tensor] = None,
+              k_weight: Optional[torch.Tensor] = None, norm_mode: int = HEAD_NORM_NONE, eps: float = 0.0,
+              cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, v_col: int = 0, v_size: int = 0,
+              v_first: Optional[torch.Tensor] = None, mix_mode: int = VALUE_MIX_NONE, lam: float = 0.0) -> None:
+    """In place on the rows of a projection buffer (csrc/rowwise.cu: head_prep_kernel): the query heads at
+    ``q_col`` and the key heads at ``k_col`` are RMS-normed (per head with weights [dim], or over the whole
+    section with weights [heads * dim]) and their first 2 * cos.shape[1] entries rotated in neighbouring
+    pairs by the tables' angles at each token's position; the values at ``v_col`` are kept in ``v_first``
+    [tokens, v_size] or blended with it, v <- (1 - lam) v + lam v_first.  All in float32."""
+    _need_cuda(x, positions, q_weight, k_weight, cos, sin, v_first)
+    if x.stride(1) != 1:
+        raise KernelError("head_prep: rows must be contiguous")
+    if norm_mode != HEAD_NORM_NONE:
+        want = (dim, dim) if norm_mode == HEAD_NORM_EACH else (q_heads * dim, k_heads * dim)
+        if q_weight is None or k_weight is None or (q_weight.numel(), k_weight.numel()) != want \
+                or q_weight.dtype != k_weight.dtype:
+            raise KernelError(f"head_prep: norm weights of {want} entries and one type")
+    pairs = 0
+    if cos is not None:
+        if sin is None or cos.shape != sin.shape or cos.dtype != torch.float32 or sin.dtype != torch.float32 \
+                or not cos.is_contiguous() or not sin.is_contiguous() or 2 * cos.shape[1] > dim:
+            raise KernelError("head_prep: cos and sin are contiguous float32 [positions, pairs], 2 * pairs <= dim")
+        pairs = cos.shape[1]
+    if mix_mode != VALUE_MIX_NONE and (v_first is None or v_first.dtype != x.dtype or not v_first.is_contiguous()
+                                       or v_first.shape[0] < tokens or v_first.shape[1] != v_size):
+        raise KernelError("head_prep: v_first must be [tokens, v_size] of the buffer's type")
+    f = _fn(_rw(), "rl_head_prep", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
+                                     c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(positions), tokens, q_col, q_heads, k_col, k_heads, dim,
+             _ptr(q_weight), _ptr(k_weight), _code(q_weight.dtype) if q_weight is not None else 0, norm_mode,
+             float(eps), _ptr(cos), _ptr(sin), pairs, cos.shape[0] if cos is not None else 0, v_col, v_size,
+             _ptr(v_first), mix_mode, float(lam), _ptr(status), _stream()), "head_prep")
+
+
 # ------------------------------------ attention with score maps, a capped score and kept first tokens
 
 def _maps(dim: int, vdim: int, maps: int) -> ctypes.CDLL:
@@ -657,15 +711,21 @@ def maps_attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcach
                      block_table: torch.Tensor, items: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                      max_parts: int, out: torch.Tensor, nitems: int, heads: int, kv_heads: int, dim: int, vdim: int,
                      maps: int, page_size: int, window: int, keep_first: int, scale: float, softcap: float,
-                     lam: float, post_scale: float, eps: float, unit_norm: bool) -> None:
+                     lam: float, post_scale: float, eps: float, unit_norm: bool,
+                     sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                     gate_mode: int = 0) -> None:
     """One query token per item (``items`` as for ``attn_decode``) over the paged cache, ``maps`` score maps
     per head over shared values (csrc/attention_maps.cu): q rows (head, map) of ``dim``, key cache
-    [pages, kv_heads * maps, page, dim], value cache [pages, kv_heads, page, vdim], out heads of ``vdim``."""
-    _need_cuda(q, kcache, vcache, out)
+    [pages, kv_heads * maps, page, dim], value cache [pages, kv_heads, page, vdim], out heads of ``vdim``.
+    ``sink`` (float32 [heads], one map only) joins every head's softmax denominator; ``gate`` (a row-strided
+    view of q's type) multiplies the output by its sigmoid, per head (``gate_mode`` 1, [tokens, heads]) or
+    per entry (2, [tokens, heads * vdim]); ``post_scale`` multiplies the output too."""
+    _need_cuda(q, kcache, vcache, out, sink, gate)
+    _check_tail(maps, heads, vdim, q, sink, gate, gate_mode)
     f = _fn(_maps(dim, vdim, maps), "rl_maps_decode",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_int,
-             c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_void_p])
     need = nitems * heads * maps * max_parts
     if part_o.numel() < need * vdim or part_ml.numel() < need * 2:
         raise KernelError("maps_attn_decode: partition workspace too small")
@@ -674,7 +734,18 @@ def maps_attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcach
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
              _ptr(items), _ptr(part_o), _ptr(part_ml), max_parts, _ptr(out), out.stride(0), nitems, heads, kv_heads,
              page_size, window, keep_first, float(scale), float(softcap), float(lam), float(post_scale), float(eps),
-             1 if unit_norm else 0, _stream()), "maps_attn_decode", 2)
+             1 if unit_norm else 0, _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             gate_mode if gate is not None else 0, _stream()), "maps_attn_decode", 2)
+
+
+def _check_tail(maps: int, heads: int, vdim: int, q: torch.Tensor, sink: Optional[torch.Tensor],
+                gate: Optional[torch.Tensor], gate_mode: int) -> None:
+    if sink is not None and (maps != 1 or sink.dtype != torch.float32 or sink.numel() != heads
+                             or not sink.is_contiguous()):
+        raise KernelError("attention_maps: a sink is float32 [heads] and goes with one score map")
+    if gate is not None and (gate_mode not in (1, 2) or gate.dtype != q.dtype or gate.stride(1) != 1
+                             or gate.shape[1] != (heads if gate_mode == 1 else heads * vdim)):
+        raise KernelError("attention_maps: a gate has the queries' type and one entry per head or per output entry")
 
 
 def maps_attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -682,19 +753,23 @@ def maps_attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcac
                       tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,
                       tile_rows_max: int, heads: int, kv_heads: int, dim: int, vdim: int, maps: int, page_size: int,
                       window: int, keep_first: int, scale: float, softcap: float, lam: float, post_scale: float,
-                      eps: float, unit_norm: bool, impl: int = 0) -> None:
+                      eps: float, unit_norm: bool, sink: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None, gate_mode: int = 0, impl: int = 0) -> None:
     """Tiles of up to ``tile_rows_max`` consecutive query tokens of one sequence; otherwise as
     ``maps_attn_decode``.  impl 0: the best kernel that applies (bfloat16 with sizes that are multiples of
     16: mma.sync tensor cores; else CUDA cores); 1: CUDA cores; 2: the tensor-core kernel or an error."""
-    _need_cuda(q, kcache, vcache, out)
+    _need_cuda(q, kcache, vcache, out, sink, gate)
+    _check_tail(maps, heads, vdim, q, sink, gate, gate_mode)
     f = _fn(_maps(dim, vdim, maps), "rl_maps_prefill",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
-             c_float, c_int, c_int, c_void_p])
+             c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
              _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions), _ptr(out), out.stride(0), tiles,
              tile_rows_max, heads, kv_heads, page_size, window, keep_first, float(scale), float(softcap), float(lam),
-             float(post_scale), float(eps), 1 if unit_norm else 0, impl, _stream()), "maps_attn_prefill")
+             float(post_scale), float(eps), 1 if unit_norm else 0, _ptr(sink), _ptr(gate),
+             gate.stride(0) if gate is not None else 0, gate_mode if gate is not None else 0, impl, _stream()),
+           "maps_attn_prefill")
 
 
 # ------------------------------------------------------- linear attention with a decaying state
@@ -737,6 +812,66 @@ def linear_attention(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, seq_
     _check(f(_code(qkv.dtype), _ptr(qkv), qkv.stride(0), q_col, k_col, v_col, _ptr(seq_of_token), _ptr(state_slot),
              _ptr(decay), _ptr(state), _ptr(out), _ptr(chunk_state) if chunked else None, tokens, sequences, heads,
              vdim, chunk, max_chunks if chunked else 1, _stream()), "linear_attention", 3 if chunked else 1)
+
+
+# ------------------------------------------------------- matrix memory with exponential gates
+
+def _mm(dim: int) -> ctypes.CDLL:
+    if not 1 <= dim <= 256:
+        raise KernelError(f"matrix_memory takes key sizes up to 256; got {dim}")
+    return _lib(f"matrix_memory_d{dim}", "matrix_memory.cu", {"RL_MM_DIM": dim})
+
+
+def matrix_memory_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of one request's state: [heads, dim, vdim + 1] (the matrix and, as one more column, the
+    normaliser) followed by [heads] stabilisers."""
+    return heads * dim * (vdim + 1) + heads
+
+
+def matrix_memory(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, q_scale: float, gates: torch.Tensor,
+                  bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor], cap: float,
+                  seq_of_token: torch.Tensor, state_slot: torch.Tensor, state: torch.Tensor, stab: torch.Tensor,
+                  num: torch.Tensor, qn: torch.Tensor, tokens: int, sequences: int, heads: int, dim: int,
+                  vdim: int) -> None:
+    """The recurrence of csrc/matrix_memory.cu over every sequence of the step, from and into the sequences'
+    state slots.  qkv [tokens, *] holds q, k (heads x dim) and v (heads x vdim) at the given columns;
+    ``gates`` float32 [tokens, 2 heads] holds the input-gate and forget-gate projections and is overwritten;
+    ``stab`` [tokens, heads], ``num`` [tokens, heads * vdim] and ``qn`` [tokens, heads] (float32) receive the
+    stabiliser, S^T q and n . q of every token."""
+    _need_cuda(qkv, gates, state, stab, num, qn)
+    for t in (gates, state, stab, num, qn, bias_i, bias_f):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError("matrix_memory: gates, biases, state and outputs are contiguous float32")
+    if qkv.stride(1) != 1 or gates.shape[1] != 2 * heads \
+            or state.shape[1] != matrix_memory_state_floats(heads, dim, vdim):
+        raise KernelError("matrix_memory: bad shapes")
+    lib = _mm(dim)
+    f = _fn(lib, "rl_memory_gates", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gates), _ptr(bias_i), _ptr(bias_f), float(cap), _ptr(seq_of_token), _ptr(state_slot), _ptr(state),
+             _ptr(stab), tokens, sequences, heads, vdim, _stream()), "matrix_memory gates")
+    f = _fn(lib, "rl_memory_recurrence", [c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_void_p])
+    _check(f(_code(qkv.dtype), _ptr(qkv), qkv.stride(0), q_col, k_col, v_col, float(q_scale), _ptr(gates),
+             _ptr(seq_of_token), _ptr(state_slot), _ptr(state), _ptr(num), _ptr(qn), tokens, sequences, heads, vdim,
+             _stream()), "matrix_memory recurrence")
+
+
+def matrix_memory_output(num: torch.Tensor, qn: torch.Tensor, stab: torch.Tensor, gate: Optional[torch.Tensor],
+                         weight: torch.Tensor, out: torch.Tensor, tokens: int, heads: int, dim: int, vdim: int,
+                         eps: float, floor: float, out_scale: float = 1.0) -> None:
+    """out = unit_rms_per_head(num / (max(|qn|, exp(-stab)) + floor)) * weight * sigmoid(gate) * out_scale;
+    ``gate`` and ``out`` are row-strided views of the activation type."""
+    _need_cuda(num, qn, stab, gate, weight, out)
+    if out.stride(1) != 1 or (gate is not None and (gate.stride(1) != 1 or gate.dtype != out.dtype)) \
+            or weight.numel() != heads * vdim:
+        raise KernelError("matrix_memory_output: bad shapes")
+    f = _fn(_mm(dim), "rl_memory_output", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                           c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    _check(f(_ptr(num), _ptr(qn), _ptr(stab), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight),
+             _code(weight.dtype), _ptr(out), out.stride(0), _code(out.dtype), tokens, heads, vdim, float(eps),
+             float(floor), float(out_scale), _stream()), "matrix_memory_output")
 
 
 # ------------------------------------------------------------------- routed feed-forward
@@ -850,10 +985,11 @@ def gather_logprob(logits: torch.Tensor, rows: int, target: torch.Tensor, out: t
            "gather_logprob")
 
 
-def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2),), linear_dims=(64,), verbose: bool = True) -> None:
+def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2), (128, 128, 1)), linear_dims=(64,), memory_dims=(64,),
+              verbose: bool = True) -> None:
     """Compiles every kernel family (attention for the given head sizes, attention with score maps for the
-    given (key size, value size, maps), linear attention for the given key sizes) and removes built files
-    of these modules that belong to other versions of the sources."""
+    given (key size, value size, maps), linear attention and the matrix memory for the given key sizes) and
+    removes built files of these modules that belong to other versions of the sources."""
     built = [
         build.compile_module("elementwise", "elementwise.cu", verbose=verbose),
         build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose),
@@ -873,4 +1009,6 @@ def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2),), linear_dims=(64,),
     for d in linear_dims:
         built.append(build.compile_module(f"linear_attention_d{d}", "linear_attention.cu", {"RL_LIN_DIM": d},
                                           verbose=verbose))
+    for d in memory_dims:
+        built.append(build.compile_module(f"matrix_memory_d{d}", "matrix_memory.cu", {"RL_MM_DIM": d}, verbose=verbose))
     build.remove_other_versions(built)

@@ -7,6 +7,16 @@ keeps the first ``keep_first`` tokens of the sequence visible; a head's output m
 mean square and multiplied by ``post_scale``.  q, k and v come from one fused projection [q | k | v] with
 optional biases; a position encoding, if the layer has one, is applied to q and k before the cache write.
 
+Further options, each with its constants as parameters: queries and keys RMS-normed with a weight before the
+rotation, per head (``head_norm`` "each": one weight of ``dim`` entries for all heads) or over the whole
+projection ("whole": weights of heads * dim entries); a rotation of the first entries of every head in
+neighbouring pairs (a ``rope_pairs`` position encoding); a sink, one learned number per head that joins the
+softmax's denominator without a key or a value; an output gate sigmoid(W_g h) per head or per entry, applied
+before the output projection (W_g is then the fourth block of the fused projection); and a blend of the
+values with those that an earlier layer of the model computed for the same token (``value_mix`` "keep" in
+the layer that provides them, "blend" in those that use them: v <- (1 - lam) v + lam v_first; what is blended
+is what is cached).
+
 The cache holds keys [kv_heads * maps, dim] and values [kv_heads, vdim] per token (a window group that
 keeps its first pages); sequences that bring one token go to the partitioned decode kernel, longer
 portions to the tiled kernel (csrc/attention_maps.cu); scores, softmax, combination and norm in float32.
@@ -44,6 +54,11 @@ class MapsAttentionParams:
     post_scale: float = 1.0      # and multiply it by this
     eps: float = 1e-6
     position: Optional[PartSpec] = None
+    head_norm: str = "none"      # none | each | whole: RMS norm of q and k with a weight, before the rotation
+    sink: bool = False           # a learned number per head in the softmax's denominator (one map)
+    gate: str = "none"           # none | head | entry: the output times sigmoid(W_g h)
+    value_mix: str = "none"      # none | keep | blend (see above)
+    value_mix_key: str = "v"     # layers that share values name the same key
 
 
 @register("mixer", "maps_attention")
@@ -59,16 +74,32 @@ class MapsAttention(Mixer):
             raise ValueError(f"attention_maps kernels take key sizes up to 256 and value sizes that are multiples "
                              f"of 4 up to 256; got dim={p.dim}, vdim={p.vdim}")
         self.position = build_part("position", p.position, rt) if p.position is not None else None
+        self.rotary = None           # (cos, sin) of an encoding that rotates neighbouring pairs
         if self.position is not None and self.position.rotary_tables() is not None:
-            raise ValueError("maps_attention applies a position encoding through its apply(); rotary tables are "
-                             "for the attention part whose cache-write kernel rotates")
+            if getattr(self.position, "pairing", None) != "neighbours":
+                raise ValueError("maps_attention rotates neighbouring pairs (rope_pairs) or applies a position "
+                                 "encoding through its apply(); tables that pair entry i with i + D/2 are for "
+                                 "the attention part whose cache-write kernel rotates")
+            self.rotary = self.position.rotary_tables()
+            if 2 * self.rotary[0].shape[1] > p.dim:
+                raise ValueError(f"a rotation of {2 * self.rotary[0].shape[1]} entries does not fit heads of {p.dim}")
+        if p.head_norm not in ("none", "each", "whole") or p.gate not in ("none", "head", "entry") \
+                or p.value_mix not in ("none", "keep", "blend"):
+            raise ValueError(f"maps_attention: head_norm '{p.head_norm}', gate '{p.gate}' or value_mix "
+                             f"'{p.value_mix}' is not known")
+        if p.sink and p.maps != 1:
+            raise ValueError("a sink goes with one score map")
         self.scale = p.scale if p.scale is not None else 1.0 / math.sqrt(p.dim)
         self.q_size = p.num_heads * p.maps * p.dim
         self.k_size = p.num_kv_heads * p.maps * p.dim
         self.v_size = p.num_kv_heads * p.vdim
         self.qkv_size = self.q_size + self.k_size + self.v_size
         self.out_size = p.num_heads * p.vdim
+        self.gate_size = {"none": 0, "head": p.num_heads, "entry": self.out_size}[p.gate]
+        self.gate_mode = {"none": 0, "head": 1, "entry": 2}[p.gate]
+        self.proj_size = self.qkv_size + self.gate_size
         self.lam = 0.0
+        self.mix = 0.0
 
     def cache_spec(self) -> CacheSpec:
         p = self.params
@@ -93,19 +124,36 @@ class MapsAttention(Mixer):
         }
         if p.maps == 2:
             t.update({n: TensorSpec((p.dim,)) for n in ("lq1", "lk1", "lq2", "lk2")})
+        if p.head_norm != "none":
+            whole = p.head_norm == "whole"
+            t["q_norm"] = TensorSpec((self.q_size if whole else p.dim,))
+            t["k_norm"] = TensorSpec((self.k_size if whole else p.dim,))
+        if p.sink:
+            t["sink"] = TensorSpec((p.num_heads,))
+        if p.gate != "none":
+            t["g"] = TensorSpec((self.gate_size, p.hidden_size))
+        if p.value_mix != "none":            # (the layer that provides the values may have the number too: unused)
+            t["vmix"] = TensorSpec((), optional=p.value_mix == "keep")
         return t
 
     def fused(self) -> Dict[str, list]:
-        return {"qkv": ["q", "k", "v"]}
+        return {"qkv": ["q", "k", "v"] + (["g"] if self.params.gate != "none" else [])}
+
+    # -- what a mixer that runs beside another one under a common output projection is asked for
+    def inner_size(self) -> int:
+        return self.out_size
+
+    def out_weight(self) -> torch.Tensor:
+        return self.w_o
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         p = self.params
         if "qkv" in tensors:
             self.w_qkv = tensors["qkv"]
         else:
-            q, k, v = tensors["q"], tensors["k"], tensors["v"]
-            dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
-            self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+            ws = [tensors[n] for n in self.fused()["qkv"]]
+            dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+            self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.w_o = tensors["o"]
         self.b_qkv = None
         if p.bias:
@@ -114,6 +162,13 @@ class MapsAttention(Mixer):
             # one number for the layer, in float32 like everything around the scores
             lq1, lk1, lq2, lk2 = (tensors[n].float() for n in ("lq1", "lk1", "lq2", "lk2"))
             self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum()) + p.diff)
+        self.w_qnorm, self.w_knorm = tensors.get("q_norm"), tensors.get("k_norm")
+        self.sink = tensors["sink"].float().contiguous() if p.sink else None
+        self.mix = float(tensors["vmix"].float()) if p.value_mix == "blend" else 0.0
+        self.norm_mode = {"none": kernels.HEAD_NORM_NONE, "each": kernels.HEAD_NORM_EACH,
+                          "whole": kernels.HEAD_NORM_WHOLE}[p.head_norm]
+        self.mix_mode = {"none": kernels.VALUE_MIX_NONE, "keep": kernels.VALUE_MIX_KEEP,
+                         "blend": kernels.VALUE_MIX_BLEND}[p.value_mix]
 
     def nbytes(self) -> int:
         return self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
@@ -121,14 +176,36 @@ class MapsAttention(Mixer):
     def forward(self, x, ctx, cache: Optional[LayerCache], state=None) -> torch.Tensor:
         p, rt = self.params, self.rt
         T = ctx.T
+        attn = rt.workspace.get("mattn.out", (rt.max_tokens, self.out_size), rt.dtype)[:T]
+        self.forward_inner(x, ctx, cache, state, attn)
+        out = rt.workspace.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        linear(attn, self.w_o, out)
+        op_mark(ctx, "o_proj", self.w_o, T)
+        return out
+
+    def forward_inner(self, x, ctx, cache: Optional[LayerCache], state, attn: torch.Tensor, scale: float = 1.0) -> None:
+        """Everything before the output projection: attn [T, heads * vdim] (possibly a view of columns of a
+        wider buffer) <- scale * the heads' gated outputs."""
+        p, rt = self.params, self.rt
+        T = ctx.T
         ws = rt.workspace
-        qkv = ws.get("mattn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
+        qkv = ws.get("mattn.qkv", (rt.max_tokens, self.proj_size), rt.dtype)[:T]
         linear(x, self.w_qkv, qkv)
         if self.b_qkv is not None:
-            kernels.bias_act(qkv, self.b_qkv, kernels.ACT_NONE)
+            kernels.bias_act(qkv, self.b_qkv, kernels.ACT_NONE, cols=self.qkv_size)
         op_mark(ctx, "qkv_proj", self.w_qkv, T)
-        if self.position is not None:
+        if self.position is not None and self.rotary is None:
             self.position.apply(qkv, p.num_heads * p.maps, p.num_kv_heads * p.maps, p.dim, ctx)
+        if self.rotary is not None or self.norm_mode != kernels.HEAD_NORM_NONE or self.mix_mode != kernels.VALUE_MIX_NONE:
+            v_first = None
+            if self.mix_mode != kernels.VALUE_MIX_NONE:
+                # (the layers run one after another within a step: the buffer holds this step's tokens)
+                v_first = ws.get("mattn.v_first." + p.value_mix_key, (rt.max_tokens, self.v_size), rt.dtype)
+            cos, sin = self.rotary if self.rotary is not None else (None, None)
+            kernels.head_prep(qkv, ctx.positions, T, 0, p.num_heads * p.maps, self.q_size, p.num_kv_heads * p.maps, p.dim,
+                              ctx.status, self.w_qnorm, self.w_knorm, self.norm_mode, p.eps, cos, sin,
+                              self.q_size + self.k_size, self.v_size, v_first, self.mix_mode, self.mix)
+            op_mark(ctx, "qk_norm+rotate", nbytes=2.0 * T * self.qkv_size * qkv.element_size())
         g = ctx.groups[cache.group]
         k_cache, v_cache = cache.tensors["k"], cache.tensors["v"]
         if cache.write:
@@ -137,25 +214,22 @@ class MapsAttention(Mixer):
             kernels.cache_store(qkv, self.q_size + self.k_size, p.num_kv_heads, p.vdim, g.slots, v_cache,
                                 rt.page_size, ctx.status, tokens=T)
             op_mark(ctx, "kv_write", nbytes=2.0 * T * (self.k_size + self.v_size) * qkv.element_size())
-        attn = ws.get("mattn.out", (rt.max_tokens, self.out_size), rt.dtype)[:T]
+        gate = qkv[:, self.qkv_size:] if self.gate_mode else None
         common = (p.num_heads, p.num_kv_heads, p.dim, p.vdim, p.maps, rt.page_size, p.window, p.keep_first,
-                  self.scale, p.softcap, self.lam, p.post_scale, p.eps, p.unit_norm)
+                  self.scale, p.softcap, self.lam, p.post_scale * scale, p.eps, p.unit_norm, self.sink, gate,
+                  self.gate_mode)
         if ctx.num_decode > 0:
             rows = ctx.max_items * p.num_heads * p.maps * ctx.parts_capacity
             part_o = ws.get("mattn.part_o", (rows * p.vdim,), torch.float32)
             part_ml = ws.get("mattn.part_ml", (rows * 2,), torch.float32)
-            kernels.maps_attn_decode(qkv, self.qkv_size, k_cache, v_cache, g.block_table, ctx.decode_info, part_o,
+            kernels.maps_attn_decode(qkv, self.proj_size, k_cache, v_cache, g.block_table, ctx.decode_info, part_o,
                                      part_ml, ctx.decode_parts, attn, ctx.num_decode, *common)
             self._mark(ctx, "attention_decode", "decode")
         if ctx.num_tiles > 0:
-            kernels.maps_attn_prefill(qkv, self.qkv_size, k_cache, v_cache, g.block_table, ctx.tile_seq, ctx.tile_tok,
+            kernels.maps_attn_prefill(qkv, self.proj_size, k_cache, v_cache, g.block_table, ctx.tile_seq, ctx.tile_tok,
                                       ctx.tile_rows, ctx.positions, attn, ctx.num_tiles, kernels.PREFILL_TILE_ROWS,
                                       *common)
             self._mark(ctx, "attention_prefill", "prefill")
-        out = ws.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
-        linear(attn, self.w_o, out)
-        op_mark(ctx, "o_proj", self.w_o, T)
-        return out
 
     def _mark(self, ctx, op: str, which: str) -> None:
         if ctx.profiler is None:

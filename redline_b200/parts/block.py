@@ -1,8 +1,11 @@
 """Pre-norm residual block: h += mixer(norm(h)); h += ffn(norm(h)), the residual
 stream h in float32 (reference: src/cuda/model/llama.cpp:116-139).  A layer without a
-feed-forward stops after the first half."""
+feed-forward stops after the first half.  Beside it the arrangements that norm a
+sublayer's output: on both sides ("sandwich") or on the output only ("outnorm")."""
 
 from __future__ import annotations
+
+import torch
 
 from .base import Block, op_mark, register
 
@@ -119,3 +122,47 @@ class SandwichBlock(Block):
         if nxt is None:
             post_norm.add_post_norm(residual, delta, None, None, rows=ctx.T)
         op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, delta, x))
+
+
+@register("block", "outnorm")
+class OutNormBlock(Block):
+    """h += norm_1(mixer(h)); h += norm_2(ffn(h)): the sublayers read the stream itself and only what they
+    put out is normed.  ``mixer_post_norm`` / ``ffn_post_norm`` are set by the model builder from the
+    layer's spec; ``mixer_norm`` and ``ffn_norm`` are None.  In a 16-bit engine the sublayers' products take
+    the stream rounded to the activation type; the kernel that adds a sublayer's normed output also writes
+    that rounded copy for the sublayer after it, across blocks too (``ctx.block_normed``), so every sublayer
+    costs one row-wise kernel.  A float32 engine hands the sublayers the stream as it is.  The block leaves
+    nothing pending."""
+
+    reads_stream = True
+    mixer_post_norm = None
+    ffn_post_norm = None
+    AS_IS = "the stream as it is"          # marks ctx.block_normed: the buffer holds the stream, not a norm of it
+
+    def parts(self):
+        return super().parts() + [p for p in (self.mixer_post_norm, self.ffn_post_norm) if p is not None]
+
+    def forward(self, residual, pending, ctx, cache, state):
+        rt = self.rt
+        T = ctx.T
+        ctx.block_hand = None
+        ready, ctx.block_normed = ctx.block_normed, None
+        copy = rt.dtype != torch.float32
+        x = rt.workspace.get("block.normed", (rt.max_tokens, residual.shape[1]), rt.dtype)[:T] if copy else residual
+        if pending is not None or (copy and not (ready is not None and ready[0] is self.AS_IS)):
+            from ..ops import kernels
+            kernels.sandwich_norm(residual, pending, None, None, x if copy else None, 0.0, kernels.NORM_RMS, rows=T)
+            op_mark(ctx, "stream_copy", nbytes=PreNormBlock._norm_bytes(residual, pending, x))
+        a = self.mixer.forward(x, ctx, cache, state)
+        last = self.ffn is None
+        nxt = copy and (not last or isinstance(ctx.block_next, OutNormBlock))
+        self.mixer_post_norm.add_post_cast(residual, a, x if nxt else None, rows=T)
+        op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, a, x))
+        if not last:
+            f = self.ffn.forward(x, ctx)
+            nxt = copy and isinstance(ctx.block_next, OutNormBlock)
+            self.ffn_post_norm.add_post_cast(residual, f, x if nxt else None, rows=T)
+            op_mark(ctx, "post_norm+add", nbytes=PreNormBlock._norm_bytes(residual, f, x))
+        if nxt:
+            ctx.block_normed = (self.AS_IS, x)
+        return None

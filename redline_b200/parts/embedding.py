@@ -1,4 +1,4 @@
-"""Token embedding (a row gather, no scaling: src/cuda/kernels/elementwise.cu:19-24)
+"""Token embedding (a row gather, src/cuda/kernels/elementwise.cu:19-24; a design may multiply the rows by a constant)
 and the output head (logits in float32: src/cuda/model/llama.cpp:143-150)."""
 
 from __future__ import annotations
@@ -18,6 +18,7 @@ from .spec import TensorSpec
 class EmbeddingParams:
     vocab_size: int
     hidden_size: int
+    scale: float = 1.0           # the rows are multiplied by this on their way into the float32 stream
 
 
 @register("embedding", "token_embedding")
@@ -35,7 +36,7 @@ class TokenEmbedding(Embedding):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, ctx, out: torch.Tensor) -> None:
-        kernels.embedding(ctx.token_ids[:ctx.T], self.weight, out, ctx.status)
+        kernels.embedding(ctx.token_ids[:ctx.T], self.weight, out, ctx.status, self.params.scale)
 
 
 @dataclass(frozen=True)

@@ -49,6 +49,12 @@ class LayerNorm(Norm):
                               out if fuse else None, self.params.eps, self.kind, rows=rows)
         return fuse
 
+    def add_post_cast(self, residual: torch.Tensor, delta: torch.Tensor, out: Optional[torch.Tensor],
+                      rows: Optional[int] = None) -> None:
+        """residual += self(delta); with ``out`` also out = the new stream rows in out's type, for a sublayer
+        that reads the stream itself."""
+        kernels.sandwich_norm(residual, delta, self.weight, None, out, self.params.eps, self.kind, rows=rows)
+
 
 @register("norm", "rmsnorm_sandwich")
 class SandwichRMSNorm(LayerNorm):

@@ -1,6 +1,8 @@
-"""SiLU-gated feed-forward: down(silu(gate(x)) * up(x)), gate and up fused into one
-projection [gate | up] (reference: src/cuda/model/llama.cpp:134-136,
-src/cuda/kernels/elementwise.cu:66-82)."""
+"""Gated feed-forward: down(act(gate(x)) * up(x)), gate and up fused into one
+projection [gate | up]; act is SiLU (reference: src/cuda/model/llama.cpp:134-136,
+src/cuda/kernels/elementwise.cu:66-82) unless the parameters name another activation
+(``gelu_tanh`` and the others of ``kernels.ACTIVATIONS``), which runs as a kernel of its
+own behind the product; the fused forms are SiLU's."""
 
 from __future__ import annotations
 
@@ -25,6 +27,7 @@ class GatedMLPParams:
     hidden_size: int
     intermediate_size: int
     bias: bool = False
+    activation: str = "silu"
 
 
 @register("ffn", "swiglu_mlp")
@@ -39,6 +42,13 @@ class SwiGLUMLP(FeedForward):
             "up_bias": TensorSpec((p.intermediate_size,), optional=not p.bias),
             "down_bias": TensorSpec((p.hidden_size,), optional=not p.bias),
         }
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if self.params.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: activation '{self.params.activation}' is not known "
+                             f"({sorted(kernels.ACTIVATIONS)})")
+        self.silu = self.params.activation == "silu"
 
     def fused(self) -> Dict[str, list]:
         return {"gate_up": ["gate", "up"]}
@@ -65,7 +75,7 @@ class SwiGLUMLP(FeedForward):
         T = ctx.T
         ws = rt.workspace
         act = ws.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
-        if T >= TC_MIN_ROWS and self.b_gate_up is None and kernels.gemm_tc_ok(x, self.w_gate_up):
+        if self.silu and T >= TC_MIN_ROWS and self.b_gate_up is None and kernels.gemm_tc_ok(x, self.w_gate_up):
             # prompt portions: gate/up product and the gated activation in one tcgen05 kernel
             kernels.gemm_tc(x, self.w_gate_up, act, kernels.EPI_SWIGLU)
         else:
@@ -73,8 +83,11 @@ class SwiGLUMLP(FeedForward):
             linear(x, self.w_gate_up, gu)
             if self.b_gate_up is not None:
                 kernels.add_bias(gu, self.b_gate_up)
-            kernels.swiglu(gu, act)
-        op_mark(ctx, "gate_up+swiglu", self.w_gate_up, T)
+            if self.silu:
+                kernels.swiglu(gu, act)
+            else:
+                kernels.gated_act(gu, act, kernels.ACTIVATIONS[self.params.activation])
+        op_mark(ctx, "gate_up+swiglu" if self.silu else "gate_up+act", self.w_gate_up, T)
         out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         linear(act, self.w_down, out)
         if self.b_down is not None:
@@ -86,7 +99,8 @@ class SwiGLUMLP(FeedForward):
         rt = self.rt
         T = ctx.T
         rms = norm.rms_params()
-        if rms is None or self.b_gate_up is not None or self.b_down is not None or rt.dtype != torch.bfloat16:
+        if (rms is None or self.b_gate_up is not None or self.b_down is not None or rt.dtype != torch.bfloat16
+                or not self.silu):
             return False
         if kernels.skinny_ok(T, self.w_gate_up, rt.dtype) and kernels.skinny_ok(T, self.w_down, rt.dtype):
             return self._into_skinny(residual, rms, ctx)

@@ -77,3 +77,42 @@ class RotaryPosition(PositionEncoding):
 @register("position", "none")
 class NoPosition(PositionEncoding):
     pass
+
+
+@dataclass(frozen=True)
+class RotaryPairsParams:
+    dims: int              # how many entries of a head are rotated: the first ``dims`` (an even number)
+    base: float
+    max_positions: int
+
+
+_pair_tables = {}          # tables shared by the parts that ask for the same ones
+
+
+@register("position", "rope_pairs")
+class RotaryPairs(PositionEncoding):
+    """Rotation of neighbouring pairs: entries (2i, 2i+1), i < dims / 2, of a head turn by the angle
+    pos * base^(-2i / dims); the entries from ``dims`` on stay as they are.  The tables hold the cosines and
+    sines [positions, dims / 2] in float32 of angles formed in double precision; the mixer applies them."""
+
+    pairing = "neighbours"
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.params
+        if p.dims <= 0 or p.dims % 2 != 0:
+            raise ValueError(f"rope_pairs rotates an even number of entries, got {p.dims}")
+        n = max(min(p.max_positions, rt.max_seq_len) if rt.max_seq_len > 0 else p.max_positions, 1)
+        key = (p.dims, float(p.base), n, str(rt.device))
+        if key not in _pair_tables:
+            freq = np.asarray([float(p.base) ** (-2.0 * i / p.dims) for i in range(p.dims // 2)], dtype=np.float64)
+            angle = np.arange(n, dtype=np.float64)[:, None] * freq[None, :]
+            _pair_tables[key] = (torch.from_numpy(np.cos(angle).astype(np.float32)).to(rt.device),
+                                 torch.from_numpy(np.sin(angle).astype(np.float32)).to(rt.device))
+        self.cos, self.sin = _pair_tables[key]
+
+    def rotary_tables(self):
+        return self.cos, self.sin
+
+    def nbytes(self) -> int:
+        return 2 * self.cos.numel() * 4

@@ -28,10 +28,12 @@ class PartSpec:
 class LayerSpec:
     """A block: how a mixer and a feed-forward are arranged around the residual
     stream.  ``arrangement`` names a registered block class.  A layer that has a mixer
-    only leaves ``ffn_norm`` and ``ffn`` out."""
+    only leaves ``ffn_norm`` and ``ffn`` out; an arrangement whose sublayers read the stream
+    itself leaves ``mixer_norm`` and ``ffn_norm`` out (None) and names the norms of the
+    sublayers' outputs."""
 
     arrangement: str
-    mixer_norm: PartSpec
+    mixer_norm: Optional[PartSpec]
     mixer: PartSpec
     ffn_norm: Optional[PartSpec] = None
     ffn: Optional[PartSpec] = None
