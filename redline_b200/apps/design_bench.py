@@ -1,5 +1,5 @@
 """Prefill and decode throughput of one architecture beside another at equal layer sizes, with the
-per-op roofline fractions of both (``bench.py --compare-design kapitar``).
+per-op roofline fractions of both (``bench.py --compare-design kapitar`` or ``pufevik``).
 
 Every size is a handful of layers whose matrices have the shapes of a real model's (random weights):
 the Kapitar model has one layer of every kind (attention + dense, lightning + routed, attention + routed,
@@ -9,6 +9,10 @@ parameters as the dense one.  Prefill: one prompt alone through ``Engine.step_to
 the call, the median of the repetitions).  Decode: ``batch`` requests decoding together through
 ``Engine.step`` (the engine's own per-step CUDA events).  Per-op: the engine's op profiler on eager steps,
 each op's bytes and operations against the measured copy bandwidth and matrix-product rate.
+
+The Pufevik model has two layers of each kind (a pair of windowed attention with a sink beside a matrix
+memory, and gated full attention with blended values; every layer with a gated feed-forward), the Llama
+model beside it the same width, number of layers, heads, kv heads, head size and feed-forward width.
 """
 
 from __future__ import annotations
@@ -24,6 +28,11 @@ SIZES: Dict[str, Dict[str, int]] = {
               lin_dim=64, vocab=32000),
     "m": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=2048,
               lin_dim=64, vocab=32000),
+}
+PUFEVIK_SIZES: Dict[str, Dict[str, int]] = {
+    # width, heads / kv heads / key and value size of both kinds of attention, feed-forward width, the memory's heads and sizes
+    "s": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, ff=2816, mem_heads=8, mem_dim=64, mem_vdim=128, vocab=32000),
+    "m": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ff=5632, mem_heads=16, mem_dim=64, mem_vdim=128, vocab=32000),
 }
 WINDOW, KEEP_FIRST = 1024, 4
 PROMPT = 2048
@@ -49,6 +58,27 @@ def llama_config(s: Dict[str, int]) -> Dict[str, Any]:
             "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": 2 * s["dim"],
             "intermediate_size": inter, "vocab_size": s["vocab"], "rope_theta": 500000.0, "rope_scaling": None,
             "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu"}
+
+
+def pufevik_config(s: Dict[str, int]) -> Dict[str, Any]:
+    heads = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5}
+    pair = {"left": dict(heads, mask={"size": WINDOW}, rot={"base": 500000.0, "dims": s["dim"] // 2}), "left_scale": 0.8,
+            "right": {"heads": s["mem_heads"], "dim": s["mem_dim"], "vdim": s["mem_vdim"], "gate_cap": 15.0}, "right_scale": 0.5}
+    full = dict(heads, rot={"base": 10000.0, "dims": s["dim"] // 2}, v_mix=True)
+    dense = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Pufevik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [{"type": "parallel", "mixer": pair, "mlp": dense}, {"type": "attention", "mixer": full, "mlp": dense},
+                       {"type": "parallel", "mixer": pair, "mlp": dense}, {"type": "attention", "mixer": full, "mlp": dense}]}
+
+
+def llama_beside_pufevik(s: Dict[str, int]) -> Dict[str, Any]:
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 4, "hidden_size": s["width"],
+            "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"],
+            "intermediate_size": s["ff"], "vocab_size": s["vocab"], "rope_theta": 500000.0, "rope_scaling": None,
+            "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192, "hidden_act": "silu"}
+
+
+DESIGNS = {"kapitar": (SIZES, kapitar_config, llama_config), "pufevik": (PUFEVIK_SIZES, pufevik_config, llama_beside_pufevik)}
 
 
 def _prefill(model: str, tokens: int, reps: int, warmup: int) -> float:
@@ -145,16 +175,19 @@ def compare(design: str, sizes: List[str], steps: int, warmup: int, batch: int, 
             with_ops: bool = True) -> Dict[str, Any]:
     from ..config import config_from_dict
     from ..weights import write_random_model
-    if design != "kapitar":
-        raise ValueError(f"no comparison is defined for '{design}' (kapitar)")
+    if design not in DESIGNS:
+        raise ValueError(f"no comparison is defined for '{design}' ({', '.join(DESIGNS)})")
+    table, design_config, beside_config = DESIGNS[design]
     out: Dict[str, Any] = {"design": design, "beside": "llama", "prompt_tokens": PROMPT, "decode_batch": batch,
                            "decode_prompt": DECODE_PROMPT, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
                            "sizes": {}}
     with tempfile.TemporaryDirectory() as tmp:
         for name in sizes:
-            s = SIZES[name]
-            entry: Dict[str, Any] = {"shape": dict(s, layers=4, window=WINDOW, keep_first=KEEP_FIRST)}
-            for arch, cfg in (("kapitar", kapitar_config(s)), ("llama", llama_config(s))):
+            s = table[name]
+            entry: Dict[str, Any] = {"shape": dict(s, layers=4, window=WINDOW)}
+            if design == "kapitar":
+                entry["shape"]["keep_first"] = KEEP_FIRST
+            for arch, cfg in ((design, design_config(s)), ("llama", beside_config(s))):
                 d = os.path.join(tmp, f"{arch}_{name}")
                 t0 = time.time()
                 write_random_model(d, config_from_dict(cfg), seed=0)

@@ -501,9 +501,9 @@ class PufevikConfig(ModelConfig):
             if att.window < 0 or layer.ff < 0:
                 raise ConfigError(f"layers[{i}]: mask.size and mlp.ff must not be negative")
             if layer.type == "attention" and att.v_mix:
-                if shared is not None and shared != att.kv_heads * att.vdim:
-                    raise ConfigError(f"layers[{i}]: layers with v_mix must have values of one size")
-                shared = att.kv_heads * att.vdim
+                if shared is not None and shared != (att.kv_heads, att.vdim):
+                    raise ConfigError(f"layers[{i}]: layers with v_mix must have values of one shape (kv_heads, vdim)")
+                shared = (att.kv_heads, att.vdim)
             if layer.type == "parallel":
                 r = layer.mixer.right
                 if r.heads <= 0 or r.dim <= 0 or r.vdim <= 0 or not r.gate_cap > 0:

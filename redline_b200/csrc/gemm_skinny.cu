@@ -58,6 +58,7 @@ struct SkinnyArgs {
   // x is such an xw, and row m of the product is scaled by rsqrt(sum(ss_in[m, 0 : ss_n]) / K + eps).
   const float* ss_in;
   int ss_n;
+  int gate_act;           // kSwiglu: what is applied to the gate, 0 SiLU, 1 the tanh form of GELU
 };
 
 
@@ -400,7 +401,10 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc, int extra_off) {
         static_cast<float*>(a.y)[o] = (rt == 0 ? early[i] : static_cast<const float*>(a.y)[o]) + __bfloat162float(__float2bfloat16_rn(v));
       } else {
         const float gt = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(u));
-        static_cast<bf16*>(a.y)[o] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
+        const float act = a.gate_act == 0
+            ? gt / (1.f + expf(-gt))
+            : 0.5f * gt * (1.f + tanhf(0.79788456080286536f * (gt + 0.044715f * gt * gt * gt)));
+        static_cast<bf16*>(a.y)[o] = __float2bfloat16_rn(act * up);
       }
     }
   }
@@ -494,7 +498,7 @@ extern "C" {
 
 int rl_gemm_skinny_max_rows() { return 16; }
 
-// epilogue: 0 bf16 store, 1 float32 store, 2 residual += y, 3 SiLU-gated product (w holds
+// epilogue: 0 bf16 store, 1 float32 store, 2 residual += y, 4 as 3 with the tanh form of GELU, 3 SiLU-gated product (w holds
 // N gate rows then N up rows).  norm != 0: x is rmsnorm(residual[rows_idx]) * norm_w.
 // Requirements: M <= 16, K a multiple of 8, 16-byte aligned rows.  Returns cudaErrorInvalidValue
 // otherwise (the caller then takes another path).
@@ -515,6 +519,11 @@ int rl_gemm_skinny_handover(const void* w, const void* x, int ldx, const float* 
   if (ss_in != nullptr && (norm || M > 8 || ss_n <= 0 || epilogue == kAddResidual))
     return static_cast<int>(cudaErrorInvalidValue);
   SkinnyArgs a;
+  a.gate_act = 0;
+  if (epilogue == 4) {            // the gated product with the tanh form of GELU on the gate
+    epilogue = kSwiglu;
+    a.gate_act = 1;
+  }
   a.next_w = next_w;
   a.next_w_f32 = next_w_f32;
   a.xw = static_cast<bf16*>(xw_out);

@@ -56,6 +56,7 @@ struct TcArgs {
   void* y;          // bf16 / float output, or the float32 residual stream
   int M, N, K, ldy;
   int n_up;         // kTcSwiglu: row of W where the up rows start (the number of gate rows)
+  int gate_act;     // kTcSwiglu: what is applied to the gate, 0 SiLU, 1 the tanh form of GELU
   int tiles_m, tiles_n;
   int group_n;      // feature tiles per group of the tile order (see tc_tile)
   int* status;
@@ -88,7 +89,12 @@ __device__ __forceinline__ void tc_drain(const TcArgs& a, uint32_t acc, int row,
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const float gt = __bfloat162float(__float2bfloat16_rn(g[i])), up = __bfloat162float(__float2bfloat16_rn(u[i]));
-        r[i] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+        if (a.gate_act == 0) {
+          r[i] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+        } else {     // 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), tanh t = 1 - 2 / (e^(2t) + 1)
+          const float t = 0.79788456080286536f * (gt + 0.044715f * gt * gt * gt);
+          r[i] = 0.5f * gt * (2.f - __fdividef(2.f, __expf(2.f * t) + 1.f)) * up;
+        }
       }
       if (row < a.M) {
         bf16* out = static_cast<bf16*>(a.y) + static_cast<size_t>(row) * a.ldy + n0 + c;
@@ -615,7 +621,7 @@ using namespace rl;
 extern "C" {
 
 // epilogue: 0 bf16 store, 1 float32 store, 2 residual (float32) += product, 3 SiLU-gated product
-// (w holds N gate rows then N up rows; y is [M, N] bfloat16).  x [M, K] and w [N or 2N, K] are
+// (w holds N gate rows then N up rows; y is [M, N] bfloat16), 4 the same gated by the tanh form of GELU.  x [M, K] and w [N or 2N, K] are
 // bfloat16 with K a multiple of 8 and 16-byte aligned rows.  status: device int, bit 0 is set if a
 // wait inside the kernel ran out.  force_bn: 0 = choose the tiling; 128 or 256 = one CTA per 128-row tile of
 // that width; 512 = CTA pairs (256 x 256 tiles, cta_group::2).
@@ -626,6 +632,11 @@ int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epil
   if (K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return static_cast<int>(cudaErrorInvalidValue);
   CUtensorMap ma, mb;
+  int gate_act = 0;
+  if (epilogue == 4) {            // the gated tile layout with another activation of the gate
+    epilogue = kTcSwiglu;
+    gate_act = 1;
+  }
   const bool gated = epilogue == kTcSwiglu;
   // pairs from two row tiles on (a single row tile would leave the peer's half of the MMA empty)
   const int bn = force_bn > 0 ? force_bn : (M > kBM ? 512 : choose_bn(M, N, epilogue, sm_count));
@@ -640,6 +651,7 @@ int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epil
     a.K = K;
     a.ldy = ldy;
     a.n_up = N;
+    a.gate_act = gate_act;
     a.status = status;
     switch (epilogue) {
       case kTcBf16: return launch_tc_pair<kTcBf16>(ma, mb, a, sm_count, stream);
@@ -657,6 +669,7 @@ int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epil
   a.K = K;
   a.ldy = ldy;
   a.n_up = N;
+  a.gate_act = gate_act;
   a.status = status;
 #define RL_TC_CASE(E)                                                                   \
   case E:                                                                               \

@@ -19,6 +19,12 @@
 // numerators S^T q (float32) and, from the extra column, n . q.  (3) output: the division, every head's
 // unit-RMS norm, the weight, the sigmoid gate and a constant factor, into the activation type.
 //
+// Long portions are cut in three passes so that a sequence is not one serial chain (the recurrence is linear
+// in the state once a_t and b_t are known): (a) every chunk of C tokens sums its own contribution to the state
+// from zero, (b) the chunks' states are chained, S_c = (product of the chunk's a_t) S_(c-1) + dS_c, (c) every
+// chunk replays its tokens from its starting state and writes the outputs.  This differs from the serial order
+// only in the rounding of the sums.
+//
 // A sequence's tokens are contiguous and in order in a step; CTAs find them by searching the step's
 // token -> sequence map.  Gates, stabiliser, state, sums and norms are float32; q, k and v are read from
 // the projection buffer in the activation type.
@@ -117,29 +123,56 @@ struct MemoryArgs {
   float* state;           // [slots] x ([heads, D, DV + 1] + [heads])
   float* num;             // [tokens, heads * DV]: S^T q
   float* qn;              // [tokens, heads]: n . q
-  int tokens;
+  float* chunk_state;     // [sequences, chunks, heads, D, DV + 1] (chunked passes only)
+  int tokens, chunk, max_chunks;
   MemoryLayout lay;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(128)
+// mode 0: the whole sequence serially from the slot's state (state written back)
+// mode 1: chunk c from zero, no outputs; the chunk's sum goes to chunk_state[seq][c]
+// mode 3: chunk c from its starting state as the chain pass left it (chunk_state[seq][c - 1]: the state after
+//         chunk c - 1; for c = 0 the slot's state, which the chain pass has copied to the entry of the last
+//         chunk, since the last chunk's CTA overwrites the slot), outputs written; the last chunk writes the slot
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
 memory_recurrence_kernel(const MemoryArgs<T> a) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[kTok][kD];
   __shared__ float ks[kTok][kD];       // b_t k_t
   __shared__ float as[kTok];
-  const int seq = blockIdx.z, head = blockIdx.y;
+  const int seq = blockIdx.z, head = blockIdx.y % a.lay.heads, c = blockIdx.y / a.lay.heads;
   const int dv = a.lay.dv;
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   const bool mine = col <= dv;         // column dv is n
-  const int t_begin = first_token_of(a.seq_of_token, a.tokens, seq);
-  const int t_end = first_token_of(a.seq_of_token, a.tokens, seq + 1);
-  if (t_begin >= t_end) return;
+  const int seq_begin = first_token_of(a.seq_of_token, a.tokens, seq);
+  const int seq_end = first_token_of(a.seq_of_token, a.tokens, seq + 1);
+  if (seq_begin >= seq_end) return;
+  int t_begin = seq_begin, t_end = seq_end;
+  if (MODE != 0) {
+    t_begin = seq_begin + c * a.chunk;
+    t_end = min(seq_end, t_begin + a.chunk);
+    if (t_begin >= seq_end) return;
+  }
+  const bool last_chunk = t_end == seq_end;
+  if (MODE == 1 && last_chunk) return;             // nobody starts from the state after the last chunk
   float* plane = a.state + static_cast<size_t>(a.state_slot[seq]) * a.lay.slot_floats() + head * a.lay.plane();
+  float* chunk_plane = a.chunk_state == nullptr ? nullptr
+      : a.chunk_state + ((static_cast<size_t>(seq) * a.max_chunks + c) * a.lay.heads + head) * a.lay.plane();
   float S[kD];
+  if (MODE == 1) {
 #pragma unroll
-  for (int i = 0; i < kD; ++i) S[i] = mine ? plane[static_cast<size_t>(i) * (dv + 1) + col] : 0.f;
+    for (int i = 0; i < kD; ++i) S[i] = 0.f;
+  } else {
+    const float* from = plane;
+    if (MODE == 3 && c > 0) from = chunk_plane - static_cast<size_t>(a.lay.heads) * a.lay.plane();
+    else if (MODE == 3 && !last_chunk) {
+      const int chunks = (seq_end - seq_begin + a.chunk - 1) / a.chunk;
+      from = chunk_plane + static_cast<size_t>(chunks - 1) * a.lay.heads * a.lay.plane();
+    }
+#pragma unroll
+    for (int i = 0; i < kD; ++i) S[i] = mine ? from[static_cast<size_t>(i) * (dv + 1) + col] : 0.f;
+  }
 
   for (int tb = t_begin; tb < t_end; tb += kTok) {
     const int nt = min(kTok, t_end - tb);
@@ -148,7 +181,7 @@ memory_recurrence_kernel(const MemoryArgs<T> a) {
       const int tt = i / kD, d = i - tt * kD;
       const T* row = a.qkv + static_cast<size_t>(tb + tt) * a.ld;
       const float b = a.gates[static_cast<size_t>(tb + tt) * (2 * a.lay.heads) + head];
-      qs[tt][d] = to_float(row[a.q_col + head * kD + d]) * a.q_scale;
+      if (MODE != 1) qs[tt][d] = to_float(row[a.q_col + head * kD + d]) * a.q_scale;
       ks[tt][d] = to_float(row[a.k_col + head * kD + d]) * b;
     }
     for (int tt = threadIdx.x; tt < nt; tt += blockDim.x)
@@ -163,15 +196,56 @@ memory_recurrence_kernel(const MemoryArgs<T> a) {
 #pragma unroll
       for (int i = 0; i < kD; ++i) {
         S[i] = fmaf(decay, S[i], ks[tt][i] * v);
-        o = fmaf(S[i], qs[tt][i], o);
+        if (MODE != 1) o = fmaf(S[i], qs[tt][i], o);
       }
-      if (col < dv) a.num[static_cast<size_t>(tb + tt) * (a.lay.heads * dv) + head * dv + col] = o;
-      else if (col == dv) a.qn[static_cast<size_t>(tb + tt) * a.lay.heads + head] = o;
+      if (MODE != 1) {
+        if (col < dv) a.num[static_cast<size_t>(tb + tt) * (a.lay.heads * dv) + head * dv + col] = o;
+        else if (col == dv) a.qn[static_cast<size_t>(tb + tt) * a.lay.heads + head] = o;
+      }
     }
   }
   if (!mine) return;
+  float* to = MODE == 1 ? chunk_plane : ((MODE == 0 || last_chunk) ? plane : nullptr);
+  if (to != nullptr) {
 #pragma unroll
-  for (int i = 0; i < kD; ++i) plane[static_cast<size_t>(i) * (dv + 1) + col] = S[i];
+    for (int i = 0; i < kD; ++i) to[static_cast<size_t>(i) * (dv + 1) + col] = S[i];
+  }
+}
+
+// The chain pass: chunk_state[seq][c] <- (product of chunk c's a_t) * (state after chunk c - 1) + chunk_state[seq][c],
+// in order of c.  One thread per element of a head's state; the products of the a_t are formed by repeated
+// multiplication in token order, as the recurrence applies them (dynamic shared memory: max_chunks floats).
+__global__ void memory_chain_kernel(const float* __restrict__ gates, const int32_t* __restrict__ seq_of_token,
+                                    const int32_t* __restrict__ state_slot, const float* __restrict__ state,
+                                    float* __restrict__ chunk_state, int tokens, int chunk, int max_chunks,
+                                    MemoryLayout lay) {
+  pdl_launch();
+  pdl_wait();
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const size_t e = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t plane = lay.plane();
+  const int t_begin = first_token_of(seq_of_token, tokens, seq);
+  const int t_end = first_token_of(seq_of_token, tokens, seq + 1);
+  const int n = t_end - t_begin;
+  const int chunks = (n + chunk - 1) / chunk;
+  // the chunks' decays side by side, a thread per chunk (every chunk before the last is full)
+  extern __shared__ float chunk_decay[];
+  for (int c = threadIdx.x; c + 1 < chunks; c += blockDim.x) {
+    float decay = 1.f;
+    for (int t = t_begin + c * chunk; t < t_begin + (c + 1) * chunk; ++t)
+      decay *= gates[static_cast<size_t>(t) * (2 * lay.heads) + lay.heads + head];
+    chunk_decay[c] = decay;
+  }
+  __syncthreads();
+  if (e >= plane) return;
+  float prev = state[static_cast<size_t>(state_slot[seq]) * lay.slot_floats() + head * plane + e];
+  if (chunks >= 2)     // the starting state of chunk 0, kept where no chunk's own sum lies
+    chunk_state[((static_cast<size_t>(seq) * max_chunks + chunks - 1) * lay.heads + head) * plane + e] = prev;
+  for (int c = 0; c + 1 < chunks; ++c) {
+    float* p = chunk_state + ((static_cast<size_t>(seq) * max_chunks + c) * lay.heads + head) * plane + e;
+    prev = fmaf(chunk_decay[c], prev, *p);
+    *p = prev;
+  }
 }
 
 // ---------------------------------------------------------------- (3) division, unit norm, weight, gate
@@ -203,6 +277,31 @@ memory_output_kernel(const float* __restrict__ num, const float* __restrict__ qn
   }
 }
 
+// chunk_state null or max_chunks <= 1: every sequence is one serial chain.  Otherwise sequences are cut into
+// chunks of `chunk` tokens (max_chunks = the most chunks any sequence of the step has) and chunk_state holds
+// [sequences, max_chunks, heads, D, DV + 1] floats.
+template <typename T>
+int launch_recurrence(const MemoryArgs<T>& a, int sequences, cudaStream_t stream) {
+  const int cols = a.lay.dv + 1, heads = a.lay.heads;
+  // one CTA for all of a head's columns while they fit 256 threads (a head of 128 values has 129 columns)
+  const int th = cols <= 256 ? (cols + 31) / 32 * 32 : 128;
+  const int col_blocks = (cols + th - 1) / th;
+  if (a.chunk_state == nullptr || a.max_chunks <= 1)
+    return static_cast<int>(launch_kernel(memory_recurrence_kernel<T, 0>, dim3(col_blocks, heads, sequences), dim3(th), 0,
+                                          stream, a));
+  cudaError_t e = launch_kernel(memory_recurrence_kernel<T, 1>, dim3(col_blocks, heads * a.max_chunks, sequences),
+                                dim3(th), 0, stream, a);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int plane = static_cast<int>(a.lay.plane());
+  e = launch_kernel(memory_chain_kernel, dim3((plane + 255) / 256, heads, sequences), dim3(256),
+                    static_cast<size_t>(a.max_chunks) * sizeof(float), stream, a.gates,
+                    a.seq_of_token, a.state_slot, static_cast<const float*>(a.state), a.chunk_state, a.tokens, a.chunk,
+                    a.max_chunks, a.lay);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(launch_kernel(memory_recurrence_kernel<T, 3>, dim3(col_blocks, heads * a.max_chunks, sequences),
+                                        dim3(th), 0, stream, a));
+}
+
 }  // namespace rl
 
 using namespace rl;
@@ -229,24 +328,22 @@ int rl_memory_gates(float* gates, const float* bias_i, const float* bias_f, floa
 
 int rl_memory_recurrence(int dtype, const void* qkv, int ld, int q_col, int k_col, int v_col, float q_scale,
                          const float* gates, const int32_t* seq_of_token, const int32_t* state_slot, float* state,
-                         float* num, float* qn, int tokens, int sequences, int heads, int dv, cudaStream_t stream) {
+                         float* num, float* qn, float* chunk_state, int tokens, int sequences, int heads, int dv,
+                         int chunk, int max_chunks, cudaStream_t stream) {
   if (tokens <= 0 || sequences <= 0) return 0;
-  const int cols = dv + 1;
-  const int th = cols >= 128 ? 128 : (cols + 31) / 32 * 32;
-  const dim3 grid((cols + th - 1) / th, heads, sequences);
 #define RL_CASE(T)                                                                                  \
   do {                                                                                              \
     MemoryArgs<T> a;                                                                                \
     a.qkv = static_cast<const T*>(qkv);                                                             \
     a.ld = ld; a.q_col = q_col; a.k_col = k_col; a.v_col = v_col; a.q_scale = q_scale;              \
     a.gates = gates; a.seq_of_token = seq_of_token; a.state_slot = state_slot; a.state = state;     \
-    a.num = num; a.qn = qn; a.tokens = tokens; a.lay = MemoryLayout{heads, dv};                     \
-    launch_kernel(memory_recurrence_kernel<T>, grid, dim3(th), 0, stream, a);                       \
+    a.num = num; a.qn = qn; a.chunk_state = chunk_state; a.tokens = tokens; a.chunk = chunk;        \
+    a.max_chunks = max_chunks; a.lay = MemoryLayout{heads, dv};                                     \
+    return launch_recurrence<T>(a, sequences, stream);                                              \
   } while (0)
   if (dtype == RL_F32) RL_CASE(float);
   else RL_CASE(bf16);
 #undef RL_CASE
-  RL_LAUNCH_END();
 }
 
 int rl_memory_output(const float* num, const float* qn, const float* stab, const void* gate, int ld_gate,

@@ -269,22 +269,28 @@ __global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restri
 //             cos[pos, i] and sin[pos, i] (tables [max_pos, rot_pairs]); the other entries stay.
 // The values (v_size entries at v_col) are, with vmix_mode 1, copied to v_first [tokens, v_size]; with
 // vmix_mode 2 replaced by (1 - lam) v + lam v_first.  A position beyond the tables sets bit 1 of *status.
+// With `slots` the finished keys and values also go to their paged caches ([pages, k_heads, page_size, dim]
+// and [pages, v_heads, page_size, v_size / v_heads]) at slots[t] = page * page_size + offset (negative: no
+// write; beyond the pool: not written, bit 2 of *status).
 struct HeadPrepArgs {
   int ld, q_col, q_heads, k_col, k_heads, dim, norm_mode;
   float eps;
   int rot_pairs, max_pos, v_col, v_size, vmix_mode;
   float lam;
+  const int32_t* slots;
+  int v_heads, page_size;
+  long long num_slots;
 };
 
 template <typename TA, typename TW>
 __global__ void head_prep_kernel(TA* __restrict__ x, const int32_t* __restrict__ positions,
                                  const TW* __restrict__ q_w, const TW* __restrict__ k_w,
                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                 TA* __restrict__ v_first, int* status, const HeadPrepArgs a) {
+                                 TA* __restrict__ v_first, TA* __restrict__ k_cache, TA* __restrict__ v_cache,
+                                 int* status, const HeadPrepArgs a) {
   pdl_launch();
   pdl_wait();
-  extern __shared__ float head_sq[];           // per head of the section: sum of squares, then the factor
-  __shared__ float scratch[32];
+  extern __shared__ float head_sq[];           // per head of both sections: the sum of squares
   const int t = blockIdx.x;
   TA* row = x + static_cast<size_t>(t) * a.ld;
   int pos = positions[t];
@@ -292,64 +298,84 @@ __global__ void head_prep_kernel(TA* __restrict__ x, const int32_t* __restrict__
     if (threadIdx.x == 0) atomicOr(status, 2);
     pos = 0;
   }
+  long long slot = a.slots != nullptr ? a.slots[t] : -1;
+  if (slot >= a.num_slots) {
+    if (threadIdx.x == 0) atomicOr(status, 4);
+    slot = -1;
+  }
+  const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int all_heads = a.q_heads + a.k_heads;
+  if (a.norm_mode != 0) {
+    for (int h = warp; h < all_heads; h += nwarps) {
+      const TA* p = h < a.q_heads ? row + a.q_col + h * a.dim : row + a.k_col + (h - a.q_heads) * a.dim;
+      float q = 0.f;
+      for (int d = lane; d < a.dim; d += 32) {
+        const float v = to_float(p[d]);
+        q += v * v;
+      }
+      q = warp_sum(q);
+      if (lane == 0) head_sq[h] = q;
+    }
+    __syncthreads();
+  }
   for (int sec = 0; sec < 2; ++sec) {
     const int heads = sec == 0 ? a.q_heads : a.k_heads;
+    const int h0 = sec == 0 ? 0 : a.q_heads;
     TA* p = row + (sec == 0 ? a.q_col : a.k_col);
     const TW* w = sec == 0 ? q_w : k_w;
-    if (heads <= 0) continue;
-    __syncthreads();
-    if (a.norm_mode != 0) {
-      for (int h = warp; h < heads; h += nwarps) {
-        float q = 0.f;
-        for (int d = lane; d < a.dim; d += 32) {
-          const float v = to_float(p[h * a.dim + d]);
-          q += v * v;
-        }
-        q = warp_sum(q);
-        if (lane == 0) head_sq[h] = q;
-      }
-      __syncthreads();
-      if (a.norm_mode == 2) {
-        float q = 0.f;
-        for (int h = threadIdx.x; h < heads; h += blockDim.x) q += head_sq[h];
-        q = block_sum(q, scratch);
-        __syncthreads();
-        const float r = rsqrtf(q / static_cast<float>(heads * a.dim) + a.eps);
-        for (int h = threadIdx.x; h < heads; h += blockDim.x) head_sq[h] = r;
-      } else {
-        for (int h = threadIdx.x; h < heads; h += blockDim.x)
-          head_sq[h] = rsqrtf(head_sq[h] / static_cast<float>(a.dim) + a.eps);
-      }
-      __syncthreads();
+    float whole = 1.f;
+    if (a.norm_mode == 2) {        // every thread adds the section's heads in the same order
+      float q = 0.f;
+      for (int h = 0; h < heads; ++h) q += head_sq[h0 + h];
+      whole = rsqrtf(q / static_cast<float>(heads * a.dim) + a.eps);
     }
+    TA* kc = (sec == 1 && slot >= 0) ? k_cache : nullptr;
     const int n = heads * a.dim;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int h = i / a.dim, d = i - h * a.dim;
       const bool paired = d < 2 * a.rot_pairs;
       if (paired && (d & 1)) continue;            // the odd entry of a pair goes with the even one
-      const float r = a.norm_mode != 0 ? head_sq[h] : 1.f;
+      const float r = a.norm_mode == 2 ? whole
+                      : (a.norm_mode == 1 ? rsqrtf(head_sq[h0 + h] / static_cast<float>(a.dim) + a.eps) : 1.f);
       const int wi = a.norm_mode == 2 ? i : d;
       float u = to_float(p[i]) * r;
       if (a.norm_mode != 0) u *= to_float(w[wi]);
+      TA* c = kc != nullptr ? kc + ((page * heads + h) * a.page_size + off) * a.dim + d : nullptr;
       if (!paired) {
-        if (a.norm_mode != 0) p[i] = from_float<TA>(u);
+        const TA o = from_float<TA>(u);
+        if (a.norm_mode != 0) p[i] = o;
+        if (c != nullptr) c[0] = o;
         continue;
       }
       float v = to_float(p[i + 1]) * r;
       if (a.norm_mode != 0) v *= to_float(w[wi + 1]);
-      const float c = cos_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
-      const float s = sin_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
-      p[i] = from_float<TA>(u * c - v * s);
-      p[i + 1] = from_float<TA>(v * c + u * s);
+      const float cs = cos_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+      const float sn = sin_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+      const TA o0 = from_float<TA>(u * cs - v * sn), o1 = from_float<TA>(v * cs + u * sn);
+      p[i] = o0;
+      p[i + 1] = o1;
+      if (c != nullptr) {
+        c[0] = o0;
+        c[1] = o1;
+      }
     }
   }
-  if (a.vmix_mode != 0) {
+  if (a.vmix_mode != 0 || slot >= 0) {
     TA* v = row + a.v_col;
-    TA* f = v_first + static_cast<size_t>(t) * a.v_size;
+    TA* f = v_first != nullptr ? v_first + static_cast<size_t>(t) * a.v_size : nullptr;
+    const int vdim = a.v_size / max(a.v_heads, 1);
     for (int i = threadIdx.x; i < a.v_size; i += blockDim.x) {
-      if (a.vmix_mode == 1) f[i] = v[i];
-      else v[i] = from_float<TA>((1.f - a.lam) * to_float(v[i]) + a.lam * to_float(f[i]));
+      TA o = v[i];
+      if (a.vmix_mode == 1) f[i] = o;
+      else if (a.vmix_mode == 2) {
+        o = from_float<TA>((1.f - a.lam) * to_float(o) + a.lam * to_float(f[i]));
+        v[i] = o;
+      }
+      if (slot >= 0) {
+        const int h = i / vdim, d = i - h * vdim;
+        v_cache[((page * a.v_heads + h) * a.page_size + off) * vdim + d] = o;
+      }
     }
   }
 }
@@ -455,19 +481,21 @@ int rl_gated_act(const void* gu, int ld, void* out, int act_dtype, int rows, int
 int rl_head_prep(void* x, int act_dtype, int ld, const int32_t* positions, int tokens, int q_col, int q_heads,
                  int k_col, int k_heads, int dim, const void* q_w, const void* k_w, int w_dtype, int norm_mode,
                  float eps, const float* cos_t, const float* sin_t, int rot_pairs, int max_pos, int v_col,
-                 int v_size, void* v_first, int vmix_mode, float lam, int* status, cudaStream_t stream) {
+                 int v_size, void* v_first, int vmix_mode, float lam, const int32_t* slots, void* k_cache,
+                 void* v_cache, int v_heads, int page_size, long long num_slots, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   HeadPrepArgs a;
   a.ld = ld; a.q_col = q_col; a.q_heads = q_heads; a.k_col = k_col; a.k_heads = k_heads; a.dim = dim;
   a.norm_mode = norm_mode; a.eps = eps; a.rot_pairs = rot_pairs; a.max_pos = max_pos; a.v_col = v_col;
   a.v_size = v_size; a.vmix_mode = vmix_mode; a.lam = lam;
+  a.slots = slots; a.v_heads = v_heads; a.page_size = page_size; a.num_slots = num_slots;
   const int widest = max(q_heads, k_heads) * dim;
   const int th = widest >= 1024 ? 512 : (widest >= 256 ? 256 : 128);
-  const size_t smem = static_cast<size_t>(max(max(q_heads, k_heads), 1)) * sizeof(float);
+  const size_t smem = static_cast<size_t>(max(q_heads + k_heads, 1)) * sizeof(float);
 #define RL_CASE(TA, TW)                                                                                          \
   launch_kernel(head_prep_kernel<TA, TW>, dim3(tokens), dim3(th), smem, stream, static_cast<TA*>(x), positions, \
                 static_cast<const TW*>(q_w), static_cast<const TW*>(k_w), cos_t, sin_t,                          \
-                static_cast<TA*>(v_first), status, a)
+                static_cast<TA*>(v_first), static_cast<TA*>(k_cache), static_cast<TA*>(v_cache), status, a)
   if (act_dtype == RL_F32) RL_CASE(float, float);
   else if (w_dtype == RL_F32) RL_CASE(bf16, float);
   else RL_CASE(bf16, bf16);

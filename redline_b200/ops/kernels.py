@@ -172,6 +172,7 @@ def gemm_tn_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Opti
 SKINNY_MAX_ROWS = 16
 SKINNY_UNSTAGED_ROWS = 8    # up to here bfloat16 activations are read from global memory, not staged
 EPI_BF16, EPI_F32, EPI_ADD_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+EPI_GEGLU_TANH = 4     # gemm_tc and gemm_skinny: as EPI_SWIGLU with the tanh form of GELU on the gate
 _sm_count: Dict[int, int] = {}
 
 
@@ -205,7 +206,8 @@ def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: O
     x given: bfloat16 activations [rows, K].  residual + norm_w given instead: x is
     bfloat16(rmsnorm(residual[rows_idx]) * norm_w) formed inside the kernel.
     epilogue EPI_BF16 / EPI_F32: store into y; EPI_ADD_RESIDUAL: y (float32 stream) += product;
-    EPI_SWIGLU: w is [2 N, K] (gate rows, then up rows), y = silu(gate) * up, [rows, N].
+    EPI_SWIGLU: w is [2 N, K] (gate rows, then up rows), y = silu(gate) * up, [rows, N]; EPI_GEGLU_TANH: the
+    same with the tanh form of GELU on the gate.
 
     The RMSNorm between a product that ends in ``residual +=`` and the product after it can be handed
     over instead of run as a kernel: with ``hand_out = (next_norm_weight, xw, sums)`` (EPI_ADD_RESIDUAL)
@@ -219,7 +221,7 @@ def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: O
              c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
              c_void_p])
     K = w.shape[1]
-    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    N = w.shape[0] // 2 if epilogue in (EPI_SWIGLU, EPI_GEGLU_TANH) else w.shape[0]
     norm = residual is not None
     if norm:
         if norm_w is None or residual.dtype != torch.float32 or residual.shape[1] != K or residual.stride(0) != K:
@@ -230,7 +232,7 @@ def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: O
             raise KernelError("gemm_skinny: x must be bfloat16 [rows, K]")
         ldx = x.stride(0)
     want = {EPI_BF16: torch.bfloat16, EPI_F32: torch.float32, EPI_ADD_RESIDUAL: torch.float32,
-            EPI_SWIGLU: torch.bfloat16}[epilogue]
+            EPI_SWIGLU: torch.bfloat16, EPI_GEGLU_TANH: torch.bfloat16}[epilogue]
     if y.dtype != want or y.shape[1] != N or y.stride(1) != 1:
         raise KernelError(f"gemm_skinny: output must be {want} [rows, {N}]")
     next_w = xw = ss_out = None
@@ -280,16 +282,17 @@ def gemm_tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16, tile_n: int = 0) -> None:
     """y = epilogue(x @ w^T) with tcgen05 tensor cores, TMEM accumulators and TMA loads
-    (csrc/gemm_tc.cu): bfloat16 x [M, K], w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up rows).
+    (csrc/gemm_tc.cu): bfloat16 x [M, K], w [N, K] (EPI_SWIGLU and EPI_GEGLU_TANH: [2 N, K], gate rows then
+    up rows).
     Epilogues as gemm_skinny's.  tile_n: 0 lets the kernel choose its tiling; 128 or 256 force one CTA per
     128-row tile of that width, 512 forces CTA pairs (tcgen05.mma.cta_group::2) on 256 x 256 tiles."""
     _need_cuda(x, w, y)
     f = _fn(_lib("gemm_tc", "gemm_tc.cu"), "rl_gemm_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     M, K = x.shape
-    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    N = w.shape[0] // 2 if epilogue in (EPI_SWIGLU, EPI_GEGLU_TANH) else w.shape[0]
     want = {EPI_BF16: torch.bfloat16, EPI_F32: torch.float32, EPI_ADD_RESIDUAL: torch.float32,
-            EPI_SWIGLU: torch.bfloat16}[epilogue]
+            EPI_SWIGLU: torch.bfloat16, EPI_GEGLU_TANH: torch.bfloat16}[epilogue]
     if w.shape[1] != K or y.dtype != want or y.shape[1] != N or y.stride(1) != 1 or not gemm_tc_ok(x, w):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
     _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(tc_status(x.device)),
@@ -665,12 +668,16 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
               k_heads: int, dim: int, status: torch.Tensor, q_weight: Optional[torch.Tensor] = None,
               k_weight: Optional[torch.Tensor] = None, norm_mode: int = HEAD_NORM_NONE, eps: float = 0.0,
               cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, v_col: int = 0, v_size: int = 0,
-              v_first: Optional[torch.Tensor] = None, mix_mode: int = VALUE_MIX_NONE, lam: float = 0.0) -> None:
+              v_first: Optional[torch.Tensor] = None, mix_mode: int = VALUE_MIX_NONE, lam: float = 0.0,
+              slots: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
+              v_cache: Optional[torch.Tensor] = None, page_size: int = 0) -> None:
     """In place on the rows of a projection buffer (csrc/rowwise.cu: head_prep_kernel): the query heads at
     ``q_col`` and the key heads at ``k_col`` are RMS-normed (per head with weights [dim], or over the whole
     section with weights [heads * dim]) and their first 2 * cos.shape[1] entries rotated in neighbouring
     pairs by the tables' angles at each token's position; the values at ``v_col`` are kept in ``v_first``
-    [tokens, v_size] or blended with it, v <- (1 - lam) v + lam v_first.  All in float32."""
+    [tokens, v_size] or blended with it, v <- (1 - lam) v + lam v_first.  All in float32.  With ``slots`` the
+    finished keys and values are also written to their paged caches ([pages, k_heads, page_size, dim] and
+    [pages, v_heads, page_size, vdim]; a slot beyond the pool is not written and sets bit 2 of ``status``)."""
     _need_cuda(x, positions, q_weight, k_weight, cos, sin, v_first)
     if x.stride(1) != 1:
         raise KernelError("head_prep: rows must be contiguous")
@@ -688,13 +695,23 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
     if mix_mode != VALUE_MIX_NONE and (v_first is None or v_first.dtype != x.dtype or not v_first.is_contiguous()
                                        or v_first.shape[0] < tokens or v_first.shape[1] != v_size):
         raise KernelError("head_prep: v_first must be [tokens, v_size] of the buffer's type")
+    v_heads, num_slots = 1, 0
+    if slots is not None:
+        if (k_cache is None or v_cache is None or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype
+                or not k_cache.is_contiguous() or not v_cache.is_contiguous() or page_size <= 0
+                or tuple(k_cache.shape[1:]) != (k_heads, page_size, dim) or v_cache.shape[2] != page_size
+                or v_cache.shape[1] * v_cache.shape[3] != v_size or v_cache.shape[0] != k_cache.shape[0]):
+            raise KernelError("head_prep: caches [pages, heads, page_size, size] of the buffer's type")
+        v_heads, num_slots = v_cache.shape[1], k_cache.shape[0] * page_size
     f = _fn(_rw(), "rl_head_prep", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
-                                     c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p])
+                                     c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                                     c_int, c_longlong, c_void_p, c_void_p])
     _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(positions), tokens, q_col, q_heads, k_col, k_heads, dim,
              _ptr(q_weight), _ptr(k_weight), _code(q_weight.dtype) if q_weight is not None else 0, norm_mode,
              float(eps), _ptr(cos), _ptr(sin), pairs, cos.shape[0] if cos is not None else 0, v_col, v_size,
-             _ptr(v_first), mix_mode, float(lam), _ptr(status), _stream()), "head_prep")
+             _ptr(v_first), mix_mode, float(lam), _ptr(slots), _ptr(k_cache), _ptr(v_cache), v_heads, page_size,
+             num_slots, _ptr(status), _stream()), "head_prep")
 
 
 # ------------------------------------ attention with score maps, a capped score and kept first tokens
@@ -832,12 +849,14 @@ def matrix_memory(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, q_scale
                   bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor], cap: float,
                   seq_of_token: torch.Tensor, state_slot: torch.Tensor, state: torch.Tensor, stab: torch.Tensor,
                   num: torch.Tensor, qn: torch.Tensor, tokens: int, sequences: int, heads: int, dim: int,
-                  vdim: int) -> None:
+                  vdim: int, chunk_state: Optional[torch.Tensor] = None, chunk: int = 0, max_chunks: int = 1) -> None:
     """The recurrence of csrc/matrix_memory.cu over every sequence of the step, from and into the sequences'
     state slots.  qkv [tokens, *] holds q, k (heads x dim) and v (heads x vdim) at the given columns;
     ``gates`` float32 [tokens, 2 heads] holds the input-gate and forget-gate projections and is overwritten;
     ``stab`` [tokens, heads], ``num`` [tokens, heads * vdim] and ``qn`` [tokens, heads] (float32) receive the
-    stabiliser, S^T q and n . q of every token."""
+    stabiliser, S^T q and n . q of every token.  With ``chunk_state`` (float32, sequences * max_chunks * heads *
+    dim * (vdim + 1)) sequences are cut into chunks of ``chunk`` tokens that run side by side
+    (``linear_attention_chunks`` says how a step is cut)."""
     _need_cuda(qkv, gates, state, stab, num, qn)
     for t in (gates, state, stab, num, qn, bias_i, bias_f):
         if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
@@ -845,17 +864,22 @@ def matrix_memory(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, q_scale
     if qkv.stride(1) != 1 or gates.shape[1] != 2 * heads \
             or state.shape[1] != matrix_memory_state_floats(heads, dim, vdim):
         raise KernelError("matrix_memory: bad shapes")
+    chunked = chunk_state is not None and max_chunks > 1
+    if chunked and (chunk_state.dtype != torch.float32
+                    or chunk_state.numel() < sequences * max_chunks * heads * dim * (vdim + 1)):
+        raise KernelError("matrix_memory: chunk workspace too small")
     lib = _mm(dim)
     f = _fn(lib, "rl_memory_gates", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(gates), _ptr(bias_i), _ptr(bias_f), float(cap), _ptr(seq_of_token), _ptr(state_slot), _ptr(state),
              _ptr(stab), tokens, sequences, heads, vdim, _stream()), "matrix_memory gates")
     f = _fn(lib, "rl_memory_recurrence", [c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
-                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_void_p])
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_void_p])
     _check(f(_code(qkv.dtype), _ptr(qkv), qkv.stride(0), q_col, k_col, v_col, float(q_scale), _ptr(gates),
-             _ptr(seq_of_token), _ptr(state_slot), _ptr(state), _ptr(num), _ptr(qn), tokens, sequences, heads, vdim,
-             _stream()), "matrix_memory recurrence")
+             _ptr(seq_of_token), _ptr(state_slot), _ptr(state), _ptr(num), _ptr(qn),
+             _ptr(chunk_state) if chunked else None, tokens, sequences, heads, vdim, chunk,
+             max_chunks if chunked else 1, _stream()), "matrix_memory recurrence", 3 if chunked else 1)
 
 
 def matrix_memory_output(num: torch.Tensor, qn: torch.Tensor, stab: torch.Tensor, gate: Optional[torch.Tensor],

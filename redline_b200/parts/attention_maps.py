@@ -202,13 +202,19 @@ class MapsAttention(Mixer):
                 # (the layers run one after another within a step: the buffer holds this step's tokens)
                 v_first = ws.get("mattn.v_first." + p.value_mix_key, (rt.max_tokens, self.v_size), rt.dtype)
             cos, sin = self.rotary if self.rotary is not None else (None, None)
+            g = ctx.groups[cache.group]
+            # (the same kernel puts the finished keys and values into the cache)
             kernels.head_prep(qkv, ctx.positions, T, 0, p.num_heads * p.maps, self.q_size, p.num_kv_heads * p.maps, p.dim,
                               ctx.status, self.w_qnorm, self.w_knorm, self.norm_mode, p.eps, cos, sin,
-                              self.q_size + self.k_size, self.v_size, v_first, self.mix_mode, self.mix)
-            op_mark(ctx, "qk_norm+rotate", nbytes=2.0 * T * self.qkv_size * qkv.element_size())
+                              self.q_size + self.k_size, self.v_size, v_first, self.mix_mode, self.mix,
+                              g.slots if cache.write else None, cache.tensors["k"], cache.tensors["v"], rt.page_size)
+            op_mark(ctx, "qk_norm+rotate+kv_write", nbytes=(2.0 * self.qkv_size + self.k_size + self.v_size) * T * qkv.element_size())
+            stored = True
+        else:
+            stored = False
         g = ctx.groups[cache.group]
         k_cache, v_cache = cache.tensors["k"], cache.tensors["v"]
-        if cache.write:
+        if cache.write and not stored:
             kernels.cache_store(qkv, self.q_size, p.num_kv_heads * p.maps, p.dim, g.slots, k_cache, rt.page_size,
                                 ctx.status, tokens=T)
             kernels.cache_store(qkv, self.q_size + self.k_size, p.num_kv_heads, p.vdim, g.slots, v_cache,

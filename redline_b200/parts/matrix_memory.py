@@ -127,9 +127,14 @@ class MatrixMemory(Mixer):
         stab = ws.get("mem.stab", (rt.max_tokens, p.num_heads), torch.float32)[:T]
         qn = ws.get("mem.qn", (rt.max_tokens, p.num_heads), torch.float32)[:T]
         num = ws.get("mem.num", (rt.max_tokens, self.v_size), torch.float32)[:T]
+        # (how a step is cut depends on its shape alone: single-token steps and full portions replay as graphs)
+        chunk, max_chunks = kernels.linear_attention_chunks(1 if ctx.num_tiles == 0 else max(ctx.host.q_len))
+        chunk_state = None
+        if max_chunks > 1:
+            chunk_state = ws.get("mem.chunks", (ctx.S * max_chunks * p.num_heads * p.dim * (p.vdim + 1),), torch.float32)
         kernels.matrix_memory(proj, 0, self.qk_size, 2 * self.qk_size, self.q_scale, gates, self.b_i, self.b_f,
                               p.gate_cap, ctx.seq_of_token, ctx.state_slot, state, stab, num, qn, T, ctx.S,
-                              p.num_heads, p.dim, p.vdim)
+                              p.num_heads, p.dim, p.vdim, chunk_state, chunk, max_chunks)
         op_mark(ctx, "matrix_memory", nbytes=T * (self.proj_size * proj.element_size() + 4.0 * self.v_size),
                 flops=4.0 * T * p.num_heads * p.dim * (p.vdim + 1))
         kernels.matrix_memory_output(num, qn, stab, proj[:, 2 * self.qk_size + self.v_size:], self.w_norm, y, T,

@@ -2,7 +2,9 @@
 projection [gate | up]; act is SiLU (reference: src/cuda/model/llama.cpp:134-136,
 src/cuda/kernels/elementwise.cu:66-82) unless the parameters name another activation
 (``gelu_tanh`` and the others of ``kernels.ACTIVATIONS``), which runs as a kernel of its
-own behind the product; the fused forms are SiLU's."""
+own behind the product; prompt portions have the tcgen05 kernel's gated epilogue for SiLU and
+the tanh GELU, and so has the weight-streaming product for at most 16 rows; the forms that also
+fuse the norm before and the add behind are SiLU's."""
 
 from __future__ import annotations
 
@@ -75,9 +77,15 @@ class SwiGLUMLP(FeedForward):
         T = ctx.T
         ws = rt.workspace
         act = ws.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
-        if self.silu and T >= TC_MIN_ROWS and self.b_gate_up is None and kernels.gemm_tc_ok(x, self.w_gate_up):
+        tc_epilogue = {"silu": kernels.EPI_SWIGLU, "gelu_tanh": kernels.EPI_GEGLU_TANH}.get(self.params.activation)
+        if (tc_epilogue is not None and T >= TC_MIN_ROWS and self.b_gate_up is None
+                and kernels.gemm_tc_ok(x, self.w_gate_up)):
             # prompt portions: gate/up product and the gated activation in one tcgen05 kernel
-            kernels.gemm_tc(x, self.w_gate_up, act, kernels.EPI_SWIGLU)
+            kernels.gemm_tc(x, self.w_gate_up, act, tc_epilogue)
+        elif (tc_epilogue is not None and self.b_gate_up is None and x.dtype == torch.bfloat16
+              and kernels.skinny_ok(T, self.w_gate_up, x.dtype) and x.stride(0) % 8 == 0):
+            # a few rows: the weight-streaming product with the gated activation in its epilogue
+            kernels.gemm_skinny(self.w_gate_up, act, tc_epilogue, T, x=x)
         else:
             gu = ws.get("ffn.gate_up", (rt.max_tokens, 2 * p.intermediate_size), rt.dtype)[:T]
             linear(x, self.w_gate_up, gu)
