@@ -13,7 +13,7 @@
 //
 // Three kernels.  (1) gates: the gate projections (float32, [tokens, 2 heads]: input gates, then forget
 // gates) get their bias, the cap c tanh(z / c) and, the forget gate, the logarithm of the sigmoid; the
-// stabiliser is carried along the sequence's tokens; a_t, b_t replace the projections and m_t goes to a
+// stabiliser is carried along the sequence's tokens (a scan, 128 tokens at a time); a_t, b_t replace the projections and m_t goes to a
 // buffer of its own.  (2) recurrence: a CTA takes one sequence, one head and a block of columns; thread j
 // keeps column j of the state (D floats) in registers, from the request's slot and back.  It writes the
 // numerators S^T q (float32) and, from the extra column, n . q.  (3) output: the division, every head's
@@ -38,7 +38,7 @@ namespace rl {
 
 constexpr int kD = RL_MM_DIM;
 static_assert(kD >= 1 && kD <= 256, "key size out of range");
-constexpr int kTok = 16;          // tokens staged in shared memory at a time
+constexpr int kTok = kD > 128 ? 8 : 16;          // tokens staged in shared memory at a time
 constexpr int kGateThreads = 128;
 
 // First token index t in [0, n) with seq_of_token[t] >= s.
@@ -69,7 +69,7 @@ memory_gates_kernel(float* __restrict__ gates, const float* __restrict__ bias_i,
                     float* __restrict__ state, float* __restrict__ stab, int tokens, MemoryLayout lay) {
   pdl_launch();
   pdl_wait();
-  __shared__ float si[kGateThreads], sf[kGateThreads], sm[kGateThreads + 1];
+  __shared__ float wi[kGateThreads / 32], wf[kGateThreads / 32], sm[kGateThreads + 1];
   const int head = blockIdx.x, seq = blockIdx.y;
   const int t_begin = first_token_of(seq_of_token, tokens, seq);
   const int t_end = first_token_of(seq_of_token, tokens, seq + 1);
@@ -85,17 +85,31 @@ memory_gates_kernel(float* __restrict__ gates, const float* __restrict__ bias_i,
       float* row = gates + static_cast<size_t>(t) * (2 * lay.heads);
       gi = capped(row[head] + bi, cap);
       gf = log_sigmoid(capped(row[lay.heads + head] + bf, cap));
-      si[threadIdx.x] = gi;
-      sf[threadIdx.x] = gf;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {           // the stabiliser along the tokens; sm[j + 1] is m after token j
-      float m = sm[0];
-      for (int j = 0; j < n; ++j) {
-        m = fmaxf(sf[j] + m, si[j]);
-        sm[j + 1] = m;
+    // The stabiliser along the tokens as a scan: token j maps m to max(f_j + m, i_j); two such maps in a row,
+    // (F1, I1) then (F2, I2), are the map (F1 + F2, max(I1 + F2, I2)).  Within a warp by shuffles, then over
+    // the warps' totals; sm[j + 1] is m after token j.
+    float F = threadIdx.x < n ? gf : 0.f, I = threadIdx.x < n ? gi : -INFINITY;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float Fp = __shfl_up_sync(0xffffffffu, F, o), Ip = __shfl_up_sync(0xffffffffu, I, o);
+      if (lane >= o) {
+        I = fmaxf(Ip + F, I);
+        F = Fp + F;
       }
     }
+    if (lane == 31) {
+      wf[warp] = F;
+      wi[warp] = I;
+    }
+    __syncthreads();
+    float PF = 0.f, PI = -INFINITY;   // the map of all tokens of the warps before this one
+    for (int w = 0; w < warp; ++w) {
+      PI = fmaxf(PI + wf[w], wi[w]);
+      PF += wf[w];
+    }
+    if (threadIdx.x < n) sm[threadIdx.x + 1] = fmaxf((PF + F) + sm[0], fmaxf(PI + F, I));
     __syncthreads();
     if (threadIdx.x < n) {
       const float m_prev = sm[threadIdx.x], m_new = sm[threadIdx.x + 1];
@@ -141,6 +155,7 @@ memory_recurrence_kernel(const MemoryArgs<T> a) {
   __shared__ float qs[kTok][kD];
   __shared__ float ks[kTok][kD];       // b_t k_t
   __shared__ float as[kTok];
+  __shared__ float vs[kTok][256];      // this thread's value of each staged token (asked for all at once)
   const int seq = blockIdx.z, head = blockIdx.y % a.lay.heads, c = blockIdx.y / a.lay.heads;
   const int dv = a.lay.dv;
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
@@ -186,11 +201,15 @@ memory_recurrence_kernel(const MemoryArgs<T> a) {
     }
     for (int tt = threadIdx.x; tt < nt; tt += blockDim.x)
       as[tt] = a.gates[static_cast<size_t>(tb + tt) * (2 * a.lay.heads) + a.lay.heads + head];
+#pragma unroll
+    for (int tt = 0; tt < kTok; ++tt) {
+      float v = col == dv ? 1.f : 0.f;
+      if (tt < nt && col < dv) v = to_float(a.qkv[static_cast<size_t>(tb + tt) * a.ld + a.v_col + head * dv + col]);
+      vs[tt][threadIdx.x] = v;
+    }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      float v = 0.f;
-      if (col < dv) v = to_float(a.qkv[static_cast<size_t>(tb + tt) * a.ld + a.v_col + head * dv + col]);
-      else if (col == dv) v = 1.f;
+      const float v = vs[tt][threadIdx.x];
       const float decay = as[tt];
       float o = 0.f;
 #pragma unroll
@@ -241,10 +260,20 @@ __global__ void memory_chain_kernel(const float* __restrict__ gates, const int32
   float prev = state[static_cast<size_t>(state_slot[seq]) * lay.slot_floats() + head * plane + e];
   if (chunks >= 2)     // the starting state of chunk 0, kept where no chunk's own sum lies
     chunk_state[((static_cast<size_t>(seq) * max_chunks + chunks - 1) * lay.heads + head) * plane + e] = prev;
-  for (int c = 0; c + 1 < chunks; ++c) {
-    float* p = chunk_state + ((static_cast<size_t>(seq) * max_chunks + c) * lay.heads + head) * plane + e;
-    prev = fmaf(chunk_decay[c], prev, *p);
-    *p = prev;
+  const size_t step = static_cast<size_t>(lay.heads) * plane;          // from a chunk's entry to the next chunk's
+  float* p = chunk_state + (static_cast<size_t>(seq) * max_chunks * lay.heads + head) * plane + e;
+  constexpr int kAhead = 8;           // the chunks' sums are asked for so many at a time, then chained
+  for (int c0 = 0; c0 + 1 < chunks; c0 += kAhead) {
+    float own[kAhead];
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) own[i] = c0 + i + 1 < chunks ? p[(c0 + i) * step] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      if (c0 + i + 1 < chunks) {
+        prev = fmaf(chunk_decay[c0 + i], prev, own[i]);
+        p[(c0 + i) * step] = prev;
+      }
+    }
   }
 }
 

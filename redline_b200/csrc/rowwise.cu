@@ -272,6 +272,22 @@ __global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restri
 // With `slots` the finished keys and values also go to their paged caches ([pages, k_heads, page_size, dim]
 // and [pages, v_heads, page_size, v_size / v_heads]) at slots[t] = page * page_size + offset (negative: no
 // write; beyond the pool: not written, bit 2 of *status).
+// Two neighbouring entries as one access (the address is a multiple of the pair's size).
+__device__ __forceinline__ void load2(const float* p, float& a, float& b) {
+  const float2 v = *reinterpret_cast<const float2*>(p);
+  a = v.x;
+  b = v.y;
+}
+__device__ __forceinline__ void load2(const bf16* p, float& a, float& b) {
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+  a = __low2float(v);
+  b = __high2float(v);
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(bf16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 struct HeadPrepArgs {
   int ld, q_col, q_heads, k_col, k_heads, dim, norm_mode;
   float eps;
@@ -280,6 +296,7 @@ struct HeadPrepArgs {
   const int32_t* slots;
   int v_heads, page_size;
   long long num_slots;
+  int pairs_ok;       // every head starts on a pair's boundary in the buffer, the weights and the caches
 };
 
 template <typename TA, typename TW>
@@ -332,6 +349,37 @@ __global__ void head_prep_kernel(TA* __restrict__ x, const int32_t* __restrict__
     }
     TA* kc = (sec == 1 && slot >= 0) ? k_cache : nullptr;
     const int n = heads * a.dim;
+    if (a.pairs_ok) {              // two entries per trip, each pair one access
+      for (int i = 2 * threadIdx.x; i < n; i += 2 * blockDim.x) {
+        const int h = i / a.dim, d = i - h * a.dim;
+        const float r = a.norm_mode == 2 ? whole
+                        : (a.norm_mode == 1 ? rsqrtf(head_sq[h0 + h] / static_cast<float>(a.dim) + a.eps) : 1.f);
+        float u, v;
+        load2(p + i, u, v);
+        if (a.norm_mode != 0) {
+          float wu, wv;
+          load2(w + (a.norm_mode == 2 ? i : d), wu, wv);
+          u *= r * wu;
+          v *= r * wv;
+        }
+        if (d < 2 * a.rot_pairs) {
+          const float cs = cos_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+          const float sn = sin_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+          const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+          u = ru;
+          v = rv;
+        } else if (a.norm_mode == 0 && kc == nullptr) {
+          continue;                  // nothing changes and nothing is cached
+        }
+        store2(p + i, u, v);
+        if (kc != nullptr) {
+          float cu, cv;              // what was stored, so that cache and buffer hold the same rounded values
+          load2(p + i, cu, cv);
+          store2(kc + ((page * heads + h) * a.page_size + off) * a.dim + d, cu, cv);
+        }
+      }
+      continue;
+    }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int h = i / a.dim, d = i - h * a.dim;
       const bool paired = d < 2 * a.rot_pairs;
@@ -489,6 +537,10 @@ int rl_head_prep(void* x, int act_dtype, int ld, const int32_t* positions, int t
   a.norm_mode = norm_mode; a.eps = eps; a.rot_pairs = rot_pairs; a.max_pos = max_pos; a.v_col = v_col;
   a.v_size = v_size; a.vmix_mode = vmix_mode; a.lam = lam;
   a.slots = slots; a.v_heads = v_heads; a.page_size = page_size; a.num_slots = num_slots;
+  const size_t pair = act_dtype == RL_F32 ? 8 : 4, wpair = (act_dtype == RL_F32 || w_dtype == RL_F32) ? 8 : 4;
+  a.pairs_ok = dim % 2 == 0 && ld % 2 == 0 && q_col % 2 == 0 && k_col % 2 == 0 &&
+               reinterpret_cast<uintptr_t>(x) % pair == 0 && reinterpret_cast<uintptr_t>(k_cache) % pair == 0 &&
+               reinterpret_cast<uintptr_t>(q_w) % wpair == 0 && reinterpret_cast<uintptr_t>(k_w) % wpair == 0;
   const int widest = max(q_heads, k_heads) * dim;
   const int th = widest >= 1024 ? 512 : (widest >= 256 ? 256 : 128);
   const size_t smem = static_cast<size_t>(max(q_heads + k_heads, 1)) * sizeof(float);
