@@ -52,6 +52,25 @@ __device__ __forceinline__ int first_token_of(const int32_t* __restrict__ seq_of
   return lo;
 }
 
+// The same for s and s + 1 at once (the two searches' loads in flight together): the sequence's tokens are [b, e).
+__device__ __forceinline__ void tokens_of(const int32_t* __restrict__ seq_of_token, int n, int s, int& b, int& e) {
+  int lo0 = 0, hi0 = n, lo1 = 0, hi1 = n;
+  while (lo0 < hi0 || lo1 < hi1) {
+    const int m0 = (lo0 + hi0) >> 1, m1 = (lo1 + hi1) >> 1;
+    const int v0 = lo0 < hi0 ? seq_of_token[m0] : 0, v1 = lo1 < hi1 ? seq_of_token[m1] : 0;
+    if (lo0 < hi0) {
+      if (v0 < s) lo0 = m0 + 1;
+      else hi0 = m0;
+    }
+    if (lo1 < hi1) {
+      if (v1 < s + 1) lo1 = m1 + 1;
+      else hi1 = m1;
+    }
+  }
+  b = lo0;
+  e = lo1;
+}
+
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float capped(float z, float cap) { return cap > 0.f ? cap * tanhf(z / cap) : z; }
 
@@ -152,16 +171,16 @@ __global__ void __launch_bounds__(256)
 memory_recurrence_kernel(const MemoryArgs<T> a) {
   pdl_launch();
   pdl_wait();
-  __shared__ float qs[kTok][kD];
-  __shared__ float ks[kTok][kD];       // b_t k_t
+  __shared__ __align__(16) float qs[kTok][kD];
+  __shared__ __align__(16) float ks[kTok][kD];       // b_t k_t
   __shared__ float as[kTok];
   __shared__ float vs[kTok][256];      // this thread's value of each staged token (asked for all at once)
   const int seq = blockIdx.z, head = blockIdx.y % a.lay.heads, c = blockIdx.y / a.lay.heads;
   const int dv = a.lay.dv;
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   const bool mine = col <= dv;         // column dv is n
-  const int seq_begin = first_token_of(a.seq_of_token, a.tokens, seq);
-  const int seq_end = first_token_of(a.seq_of_token, a.tokens, seq + 1);
+  int seq_begin, seq_end;
+  tokens_of(a.seq_of_token, a.tokens, seq, seq_begin, seq_end);
   if (seq_begin >= seq_end) return;
   int t_begin = seq_begin, t_end = seq_end;
   if (MODE != 0) {
@@ -212,10 +231,34 @@ memory_recurrence_kernel(const MemoryArgs<T> a) {
       const float v = vs[tt][threadIdx.x];
       const float decay = as[tt];
       float o = 0.f;
+      float o1 = 0.f, o2 = 0.f, o3 = 0.f;        // four sums side by side: one chain of kD dependent adds would be the limit
+      if (kD % 4 == 0) {
+        // keys and queries four at a time: every lane reads the same words, and one 16-byte read serves four
+        // updates (read one by one, the shared-memory pipe is the limit, not the arithmetic)
+        const float4* k4 = reinterpret_cast<const float4*>(ks[tt]);
+        const float4* q4 = reinterpret_cast<const float4*>(qs[tt]);
 #pragma unroll
-      for (int i = 0; i < kD; ++i) {
-        S[i] = fmaf(decay, S[i], ks[tt][i] * v);
-        if (MODE != 1) o = fmaf(S[i], qs[tt][i], o);
+        for (int i = 0; i < kD / 4; ++i) {
+          const float4 kk = k4[i];
+          S[4 * i] = fmaf(decay, S[4 * i], kk.x * v);
+          S[4 * i + 1] = fmaf(decay, S[4 * i + 1], kk.y * v);
+          S[4 * i + 2] = fmaf(decay, S[4 * i + 2], kk.z * v);
+          S[4 * i + 3] = fmaf(decay, S[4 * i + 3], kk.w * v);
+          if (MODE != 1) {
+            const float4 qq = q4[i];
+            o = fmaf(S[4 * i], qq.x, o);
+            o1 = fmaf(S[4 * i + 1], qq.y, o1);
+            o2 = fmaf(S[4 * i + 2], qq.z, o2);
+            o3 = fmaf(S[4 * i + 3], qq.w, o3);
+          }
+        }
+        o = (o + o1) + (o2 + o3);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kD; ++i) {
+          S[i] = fmaf(decay, S[i], ks[tt][i] * v);
+          if (MODE != 1) o = fmaf(S[i], qs[tt][i], o);
+        }
       }
       if (MODE != 1) {
         if (col < dv) a.num[static_cast<size_t>(tb + tt) * (a.lay.heads * dv) + head * dv + col] = o;
