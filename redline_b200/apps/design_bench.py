@@ -62,11 +62,11 @@ def llama_config(s: Dict[str, int]) -> Dict[str, Any]:
 
 def pufevik_config(s: Dict[str, int]) -> Dict[str, Any]:
     heads = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5}
-    pair = {"left": dict(heads, mask={"size": WINDOW}, rot={"base": 500000.0, "dims": s["dim"] // 2}), "left_scale": 0.8,
-            "right": {"heads": s["mem_heads"], "dim": s["mem_dim"], "vdim": s["mem_vdim"], "gate_cap": 15.0}, "right_scale": 0.5}
+    pair = {"left": dict(heads, mask={"size": WINDOW}, rot={"base": 1000000.0, "dims": s["dim"] // 2}), "left_scale": 0.7,
+            "right": {"heads": s["mem_heads"], "dim": s["mem_dim"], "vdim": s["mem_vdim"], "gate_cap": 12.0}, "right_scale": 0.6}
     full = dict(heads, rot={"base": 10000.0, "dims": s["dim"] // 2}, v_mix=True)
     dense = {"kind": "dense", "ff": s["ff"]}
-    return {"architecture": "Pufevik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+    return {"architecture": "Pufevik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
             "layers": [{"type": "parallel", "mixer": pair, "mlp": dense}, {"type": "attention", "mixer": full, "mlp": dense},
                        {"type": "parallel", "mixer": pair, "mlp": dense}, {"type": "attention", "mixer": full, "mlp": dense}]}
 

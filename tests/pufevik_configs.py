@@ -18,7 +18,7 @@ def attention(heads, kv_heads, dim, vdim, rot_dims, base=10000.0, v_mix=False, s
             "scale": scale if scale is not None else dim ** -0.5, "rot": {"base": base, "dims": rot_dims}}
 
 
-def windowed(heads, kv_heads, dim, vdim, rot_dims, size, base=500000.0, scale=None):
+def windowed(heads, kv_heads, dim, vdim, rot_dims, size, base=200000.0, scale=None):
     return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": size},
             "scale": scale if scale is not None else dim ** -0.5, "rot": {"base": base, "dims": rot_dims}}
 
@@ -36,10 +36,10 @@ def dense(ff):
 
 
 MIX = {
-    "architecture": "Pufevik", "vocab": 149, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.7},
+    "architecture": "Pufevik", "vocab": 149, "width": 96, "norm": {"eps": 3e-6}, "embedding": {"scale": 0.7},
     "layers": [
         {"type": "attention", "mixer": attention(4, 2, 32, 16, 32, v_mix=True, scale=0.3), "mlp": dense(160)},
-        {"type": "parallel", "mixer": pair(windowed(4, 2, 16, 32, 8, 24), memory(3, 16, 24, 15.0), 0.8, 0.5), "mlp": dense(72)},
+        {"type": "parallel", "mixer": pair(windowed(4, 2, 16, 32, 8, 24), memory(3, 16, 24, 12.0), 0.9, 0.4), "mlp": dense(72)},
         {"type": "attention", "mixer": attention(2, 2, 48, 16, 2, base=500.0, v_mix=True), "mlp": None},
         {"type": "parallel", "mixer": pair(windowed(3, 3, 32, 16, 32, 7, base=100.0), memory(1, 32, 64, 4.0), 1.0, 1.0), "mlp": dense(64)},
         {"type": "attention", "mixer": attention(3, 3, 16, 48, 8, v_mix=False), "mlp": dense(40)},
@@ -58,7 +58,7 @@ ODD = {
 }
 
 ATTN = {
-    "architecture": "Pufevik", "vocab": 101, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
+    "architecture": "Pufevik", "vocab": 101, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.6},
     "layers": [
         {"type": "attention", "mixer": attention(4, 2, 16, 16, 8, v_mix=False), "mlp": dense(96)},
         {"type": "attention", "mixer": attention(2, 2, 32, 32, 32, v_mix=True), "mlp": dense(96)},
@@ -69,8 +69,8 @@ ATTN = {
 MEM = {
     "architecture": "Pufevik", "vocab": 83, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5},
     "layers": [
-        {"type": "parallel", "mixer": pair(windowed(2, 2, 16, 16, 8, 1), memory(2, 32, 48, 15.0), 0.2, 1.0), "mlp": dense(96)},
-        {"type": "parallel", "mixer": pair(windowed(2, 1, 16, 16, 8, 1), memory(4, 16, 16, 15.0), 0.2, 1.0), "mlp": None},
+        {"type": "parallel", "mixer": pair(windowed(2, 2, 16, 16, 8, 1), memory(2, 32, 40, 10.0), 0.2, 1.0), "mlp": dense(96)},
+        {"type": "parallel", "mixer": pair(windowed(2, 1, 16, 16, 8, 1), memory(4, 16, 16, 20.0), 0.2, 1.0), "mlp": None},
     ],
 }
 
@@ -81,7 +81,7 @@ def one_windowed_layer(size, heads=2, kv_heads=1, dim=32, vdim=32, rot_dims=8):
     """One pair whose memory side is switched off by its scale: what the window shows decides the logits."""
     return {"architecture": "Pufevik", "vocab": 67, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
             "layers": [{"type": "parallel", "mlp": None,
-                        "mixer": pair(windowed(heads, kv_heads, dim, vdim, rot_dims, size), memory(1, 8, 8, 15.0), 1.0, 0.0)}]}
+                        "mixer": pair(windowed(heads, kv_heads, dim, vdim, rot_dims, size), memory(1, 8, 8, 9.0), 1.0, 0.0)}]}
 
 
 def one_attention_layer(heads=4, kv_heads=2, dim=16, vdim=48, rot_dims=4):

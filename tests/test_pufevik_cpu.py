@@ -28,7 +28,7 @@ def test_configuration_round_trip_and_registry(tmp_path):
         assert load_config(str(tmp_path / name)) == c
     m = config_from_dict(C.MIX)
     assert m.layers[0].mixer.v_mix and not m.layers[4].mixer.v_mix and m.layers[2].ff == 0
-    assert m.layers[1].mixer.left.window == 24 and m.layers[1].mixer.right.gate_cap == 15.0
+    assert m.layers[1].mixer.left.window == 24 and m.layers[1].mixer.right.gate_cap == 12.0
     assert m.layers[3].mixer.left.rot.base == 100.0 and m.layers[6].mixer.right_scale == 1.7
 
 
