@@ -321,7 +321,7 @@ __global__ void memory_chain_kernel(const float* __restrict__ gates, const int32
 }
 
 // ---------------------------------------------------------------- (3) division, unit norm, weight, gate
-// One CTA per token, a warp per head in turn.
+// A warp per (token, head): a CTA takes one token and as many heads as it has warps.
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128)
 memory_output_kernel(const float* __restrict__ num, const float* __restrict__ qn, const float* __restrict__ stab,
@@ -331,7 +331,7 @@ memory_output_kernel(const float* __restrict__ num, const float* __restrict__ qn
   pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int h = warp; h < heads; h += nwarps) {
+  for (int h = blockIdx.y * nwarps + warp; h < heads; h += gridDim.y * nwarps) {
     const float den = fmaxf(fabsf(qn[static_cast<size_t>(t) * heads + h]), expf(-stab[static_cast<size_t>(t) * heads + h])) + floor;
     const float* o = num + static_cast<size_t>(t) * heads * dv + h * dv;
     float q = 0.f;
@@ -423,7 +423,7 @@ int rl_memory_output(const float* num, const float* qn, const float* stab, const
                      float eps, float floor, float out_scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
 #define RL_CASE(TA, TW)                                                                                          \
-  launch_kernel(memory_output_kernel<TA, TW>, dim3(tokens), dim3(128), 0, stream, num, qn, stab,                \
+  launch_kernel(memory_output_kernel<TA, TW>, dim3(tokens, (heads + 3) / 4), dim3(128), 0, stream, num, qn, stab, \
                 static_cast<const TA*>(gate), ld_gate, static_cast<const TW*>(w), static_cast<TA*>(out), ld_out, \
                 heads, dv, eps, floor, out_scale)
   if (act_dtype == RL_F32) RL_CASE(float, float);

@@ -91,3 +91,44 @@ def one_attention_layer(heads=4, kv_heads=2, dim=16, vdim=48, rot_dims=4):
 
 def clone(cfg):
     return copy.deepcopy(cfg)
+
+
+def random_config(seed, big=False):
+    """A configuration drawn from a seed: two to five layers of either kind with sizes of their own (``big``: head
+    sizes of 128 to 256), windows from one token to longer than the test sequences, layers with and without a
+    feed-forward; the layers that share values have one value shape."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([256, 320] if big else [64, 96, 128, 160])
+    shared = None
+
+    def heads(window):
+        kv = rng.choice([1, 2, 3])
+        dim = rng.choice([128, 192, 256] if big else [16, 24, 32, 48, 64, 80])
+        m = {"heads": kv * rng.choice([1, 2, 4]), "kv_heads": kv, "dim": dim,
+             "vdim": rng.choice([128, 176, 256] if big else [8, 16, 24, 40, 64, 96]),
+             "scale": dim ** -0.5 * rng.choice([0.7, 1.0, 1.3]),
+             "rot": {"base": rng.choice([100.0, 10000.0, 1e6]), "dims": max(2, rng.choice([2, dim // 4 * 2, dim // 2 * 2]))}}
+        if window:
+            m["mask"] = {"size": rng.choice([1, 3, 17, 64, 100, 300])}
+        return m
+
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        if rng.random() < 0.5:
+            m = heads(False)
+            m["v_mix"] = rng.random() < 0.7
+            if m["v_mix"] and shared is None:
+                shared = (m["kv_heads"], m["vdim"])
+            elif m["v_mix"]:
+                m["kv_heads"], m["vdim"] = shared
+                m["heads"] = shared[0] * rng.choice([1, 2])
+            layer = {"type": "attention", "mixer": m}
+        else:
+            right = memory(rng.choice([1, 2, 3, 5]), rng.choice([128, 256] if big else [8, 16, 32, 64]),
+                           rng.choice([128, 256] if big else [8, 20, 48, 64, 130]), rng.choice([3.0, 10.0, 25.0]))
+            layer = {"type": "parallel", "mixer": pair(heads(True), right, rng.choice([0.3, 1.0, 1.4]), rng.choice([0.5, 1.0, 2.0]))}
+        layer["mlp"] = None if rng.random() < 0.25 else dense(rng.choice([40, 96, 200, 264]))
+        layers.append(layer)
+    return {"architecture": "Pufevik", "vocab": rng.choice([50, 131, 300]), "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5])},
+            "embedding": {"scale": rng.choice([0.4, 1.0, 2.0])}, "layers": layers}

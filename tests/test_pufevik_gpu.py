@@ -350,6 +350,28 @@ def test_a_prompt_long_enough_for_the_memory_to_run_in_chunks(dtype, models, eng
     check(np.concatenate(outs), cfg, w, toks, dtype, ref=ref)
 
 
+@pytest.mark.parametrize("seed,big", [(1, False), (2, False), (5, False), (8, False), (11, False), (6, True)])
+def test_configurations_drawn_at_random(seed, big, tmp_path):
+    """Other layer orders, head counts, sizes, windows and constants: a prompt in portions with single tokens
+    between them, then whole, in both engine types."""
+    cfg = C.random_config(seed, big)
+    toks = random_tokens(cfg["vocab"], 330, seed)
+    for dtype in ("float32", "bfloat16"):
+        d, w = make_model(tmp_path, cfg, seed + (0 if dtype == "float32" else 100), sharpen=1.5)
+        eng = engine_for(d, dtype)
+        ref = Reference(cfg, w, toks, dtype)
+        outs, i = [], 0
+        for s in (130, 2, 1, 70, 1, 1, 1, 3, 121):
+            outs.append(eng.step_tokens([("p", toks[i:i + s], list(range(s)))]).cpu().numpy())
+            i += s
+        eng.close_request("p")
+        check(np.concatenate(outs), cfg, w, toks, dtype, ref=ref)
+        whole = eng.step_tokens([("w", toks, list(range(len(toks))))]).cpu().numpy()
+        eng.close_request("w")
+        check(whole, cfg, w, toks, dtype, ref=ref)
+        del eng
+
+
 def test_decoding_as_cuda_graphs(models, engines):
     """Single-token steps padded and replayed as CUDA graphs: attention layers only, and the model whose
     layers keep a state (the padding rows have a state slot of their own)."""
