@@ -36,7 +36,8 @@ namespace rl {
 
 constexpr int kD = RL_QK_DIM, kDV = RL_V_DIM, kM = RL_MAPS;
 static_assert(kM == 1 || kM == 2, "one or two score maps");
-static_assert(kD >= 1 && kD <= 256 && kDV >= 4 && kDV <= 256 && kDV % 4 == 0, "sizes out of range");
+static_assert(kD >= 1 && kD <= 256 && kDV >= 1 && kDV <= 256, "sizes out of range");
+constexpr int kVQ = (kDV + 3) / 4;             // value columns of one of the four threads that share a query row
 constexpr int kPart = 128;
 constexpr int kThreads = 128;
 constexpr int kLPK = 8;                      // lanes that share a key
@@ -371,9 +372,9 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
   const int k_end = pos0 + rows;     // exclusive
   const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
 
-  float o[kDV / 4];
+  float o[kVQ];
 #pragma unroll
-  for (int i = 0; i < kDV / 4; ++i) o[i] = 0.f;
+  for (int i = 0; i < kVQ; ++i) o[i] = 0.f;
 
   for (int m = 0; m < kM; ++m) {
     __syncthreads();
@@ -384,9 +385,9 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
                                    : 0.f;
     }
     float mx = -INFINITY, l = 0.f;
-    float acc[kDV / 4];
+    float acc[kVQ];
 #pragma unroll
-    for (int i = 0; i < kDV / 4; ++i) acc[i] = 0.f;
+    for (int i = 0; i < kVQ; ++i) acc[i] = 0.f;
 
     for (int k0 = 0; k0 < k_end; k0 += kBK) {
       // a tile that no row of this CTA sees is skipped: the rows' windows together reach back to
@@ -451,11 +452,12 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
       mx = m_new;
       __syncwarp();
 #pragma unroll
-      for (int i = 0; i < kDV / 4; ++i) acc[i] *= alpha;
+      for (int i = 0; i < kVQ; ++i) acc[i] *= alpha;
       for (int c = 0; c < kBK; ++c) {
         const float p = Ps[r * (kBK + 1) + c];
 #pragma unroll
-        for (int i = 0; i < kDV / 4; ++i) acc[i] += p * Vs[c * kDV + cq + 4 * i];
+        for (int i = 0; i < kVQ; ++i)
+          if (kDV % 4 == 0 || cq + 4 * i < kDV) acc[i] += p * Vs[c * kDV + cq + 4 * i];
       }
     }
     if (kM == 1 && a.tail.sink != nullptr && mx != -INFINITY) {
@@ -465,26 +467,27 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
       const float alpha = expf(mx - m_new);
       l = l * alpha + expf(sk - m_new);
 #pragma unroll
-      for (int i = 0; i < kDV / 4; ++i) acc[i] *= alpha;
+      for (int i = 0; i < kVQ; ++i) acc[i] *= alpha;
     }
     const float coef = (m == 0 ? 1.f : -a.lambda) / (l > 0.f ? l : 1.f);
 #pragma unroll
-    for (int i = 0; i < kDV / 4; ++i) o[i] += coef * acc[i];
+    for (int i = 0; i < kVQ; ++i) o[i] += coef * acc[i];
   }
   float scale_out = a.post_scale;
   if (a.unit_norm) {
     float q = 0.f;
 #pragma unroll
-    for (int i = 0; i < kDV / 4; ++i) q += o[i] * o[i];
+    for (int i = 0; i < kVQ; ++i) q += o[i] * o[i];
     q += __shfl_xor_sync(0xffffffffu, q, 1);
     q += __shfl_xor_sync(0xffffffffu, q, 2);
     scale_out *= rsqrtf(q / static_cast<float>(kDV) + a.eps);
   }
   if (r < rows) {
 #pragma unroll
-    for (int i = 0; i < kDV / 4; ++i)
-      a.out[static_cast<size_t>(tok0 + r) * a.out_stride + head * kDV + cq + 4 * i] =
-          from_float<T>(o[i] * scale_out * gate_factor(a.tail, tok0 + r, head, cq + 4 * i, kDV));
+    for (int i = 0; i < kVQ; ++i)
+      if (kDV % 4 == 0 || cq + 4 * i < kDV)
+        a.out[static_cast<size_t>(tok0 + r) * a.out_stride + head * kDV + cq + 4 * i] =
+            from_float<T>(o[i] * scale_out * gate_factor(a.tail, tok0 + r, head, cq + 4 * i, kDV));
   }
 }
 

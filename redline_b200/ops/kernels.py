@@ -717,9 +717,9 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
 # ------------------------------------ attention with score maps, a capped score and kept first tokens
 
 def _maps(dim: int, vdim: int, maps: int) -> ctypes.CDLL:
-    if not (1 <= dim <= 256 and 4 <= vdim <= 256 and vdim % 4 == 0 and maps in (1, 2)):
-        raise KernelError(f"attention_maps takes key sizes up to 256, value sizes that are multiples of 4 up to 256 "
-                          f"and one or two maps; got {dim}, {vdim}, {maps}")
+    if not (1 <= dim <= 256 and 1 <= vdim <= 256 and maps in (1, 2)):
+        raise KernelError(f"attention_maps takes key and value sizes up to 256 and one or two maps; "
+                          f"got {dim}, {vdim}, {maps}")
     return _lib(f"attention_maps_d{dim}_v{vdim}_m{maps}", "attention_maps.cu",
                 {"RL_QK_DIM": dim, "RL_V_DIM": vdim, "RL_MAPS": maps})
 

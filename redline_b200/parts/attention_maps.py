@@ -70,9 +70,8 @@ class MapsAttention(Mixer):
             raise ValueError(f"num_heads {p.num_heads} is no multiple of num_kv_heads {p.num_kv_heads}")
         if p.maps not in (1, 2):
             raise ValueError(f"attention with {p.maps} score maps is not supported (1 or 2)")
-        if not (1 <= p.dim <= 256 and 4 <= p.vdim <= 256 and p.vdim % 4 == 0):
-            raise ValueError(f"attention_maps kernels take key sizes up to 256 and value sizes that are multiples "
-                             f"of 4 up to 256; got dim={p.dim}, vdim={p.vdim}")
+        if not (1 <= p.dim <= 256 and 1 <= p.vdim <= 256):
+            raise ValueError(f"attention_maps kernels take key and value sizes up to 256; got dim={p.dim}, vdim={p.vdim}")
         self.position = build_part("position", p.position, rt) if p.position is not None else None
         self.rotary = None           # (cos, sin) of an encoding that rotates neighbouring pairs
         if self.position is not None and self.position.rotary_tables() is not None:

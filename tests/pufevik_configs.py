@@ -52,8 +52,8 @@ ODD = {
     "architecture": "Pufevik", "vocab": 61, "width": 100, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
     "layers": [
         {"type": "parallel", "mixer": pair(windowed(3, 1, 20, 12, 6, 11), memory(2, 10, 20, 8.0), 1.2, 0.6), "mlp": dense(28)},
-        {"type": "attention", "mixer": attention(2, 2, 10, 4, 10, v_mix=True), "mlp": dense(36)},
-        {"type": "attention", "mixer": attention(4, 2, 12, 4, 4, v_mix=True), "mlp": None},
+        {"type": "attention", "mixer": attention(2, 2, 10, 6, 10, v_mix=True), "mlp": dense(36)},
+        {"type": "attention", "mixer": attention(4, 2, 13, 6, 4, v_mix=True), "mlp": None},
     ],
 }
 

@@ -317,7 +317,7 @@ def test_a_far_key_among_hundreds(dtype, tmp_path):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sizes_that_are_no_multiples_of_8(dtype, models, engines):
-    """Width 100, key sizes 20, 10 and 12, value sizes 12, 4 and 20: no 16-byte pieces, no tensor-core tiles; a
+    """Width 100, key sizes 20, 10 and 13, value sizes 12, 6 and 20: no 16-byte pieces, no tensor-core tiles; a
     prompt in portions, then single tokens."""
     eng, (_, w) = engines("odd", dtype), models["odd", dtype]
     cfg = C.ODD

@@ -145,7 +145,8 @@ def test_heads_between_projection_and_cache(dtype, tol, H, G, D, DV, rot, mode):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,DV,size,sink,gate", [
     (4, 1, 80, 32, 56, True, 1), (4, 2, 16, 48, 24, True, 1), (2, 2, 32, 16, 0, False, 2), (8, 2, 64, 64, 130, True, 2),
-    (3, 3, 20, 12, 9, True, 1), (2, 1, 112, 80, 0, False, 2), (2, 2, 16, 16, 1, True, 0)])
+    (3, 3, 20, 12, 9, True, 1), (2, 1, 112, 80, 0, False, 2), (2, 2, 16, 16, 1, True, 0), (2, 1, 7, 5, 30, True, 2),
+    (4, 2, 33, 18, 0, True, 1)])
 def test_attention_with_a_sink_and_a_gate_over_shuffled_pages(dtype, H, G, D, DV, size, sink, gate):
     """A portion of 150 tokens after 70 cached ones and, in the same cache, single tokens at several contexts,
     over pages handed out in a shuffled order; cache rows that no query may read hold NaN.  One sink is made
